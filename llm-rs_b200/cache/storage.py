@@ -74,7 +74,7 @@ class CacheStorage:
         self.state: List[Dict[str, torch.Tensor]] = []
         for s, (_, st) in enumerate(needs):
             tensors = {}
-            if st is not None and self.run_order[s].cache_of is None:
+            if st is not None:      # an entry that reads another's cache still owns what its block asked for
                 for name, shape in st.tensors.items():
                     tensors[name] = torch.zeros((n_slots, *shape), dtype=torch.float32, device=device)
             self.state.append(tensors)
@@ -104,7 +104,7 @@ class CacheStorage:
     def layer_cache(self, s: int, block_tables: Sequence[Optional[torch.Tensor]]) -> LayerCache:
         g, i = self.entry_group[s], self.entry_index[s]
         src = self.run_order[s].cache_of
-        state = self.state[s if src is None else src]
+        state = self.state[s] if src is None else {**self.state[src], **self.state[s]}
         if g is None:
             return LayerCache(None, None, None, self.page_size, src is None, state, None)
         kv, planes = self._views(g, i)

@@ -3,6 +3,7 @@ from .errors import ConfigError
 from .registry import (ArchitectureEntry, architecture_names, load_config,
                        register_architecture, resolve_architecture, unregister_architecture)
 from .qwen3 import Qwen3Config
+from .rusadra import RusadraConfig
 
 __all__ = ["ConfigError", "ArchitectureEntry", "architecture_names", "load_config",
-           "register_architecture", "resolve_architecture", "unregister_architecture", "Qwen3Config"]
+           "register_architecture", "resolve_architecture", "unregister_architecture", "Qwen3Config", "RusadraConfig"]

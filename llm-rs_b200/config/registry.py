@@ -51,6 +51,8 @@ def architecture_names() -> List[str]:
 def resolve_architecture(raw: Dict[str, Any]) -> ArchitectureEntry:
     """Pick the registry entry for a parsed config.json."""
     names = raw.get("architectures")
+    if names is None and isinstance(raw.get("architecture"), str):     # some designs name themselves in one string
+        names = [raw["architecture"]]
     if isinstance(names, list) and names:
         name = names[0]
         if name in _ARCHITECTURES:
@@ -79,4 +81,9 @@ def load_config(model_dir: str):
     if not isinstance(raw, dict):
         raise ConfigError(f"{path} must hold a JSON object")
     entry = resolve_architecture(raw)
+    if getattr(entry.config_cls, "wants_tensor_shapes", False):
+        # A design whose config.json leaves some sizes to the tensors' shapes: only the files' headers are read.
+        from ..weights.safetensors_io import open_model_files
+        shapes = {name: f.shape(name) for f in open_model_files(model_dir) for name in f.names()}
+        return entry, entry.config_cls.from_dict(raw, tensor_shapes=shapes)
     return entry, entry.config_cls.from_dict(raw)

@@ -1,0 +1,250 @@
+// Latent attention: every token caches ONE row shared by all heads, a normed latent c [rank] and a rotated key
+// part kr [rot], in pages of two planes ([page_size, rank] then [page_size, rot] per page). With the per-head key
+// up-projection folded into the query (qa_h = W_uk,h^T q_h, made by a batched product before this kernel) a head's
+// score against key j is (qa_h . c_j + qr_h . kr_j) * scale, and its output is W_uv,h (sum_j p_j c_j): the kernel
+// only ever reads the cached rows, each once for all the heads of a group.
+//
+//   latent_prepare    per token: rotates the rot part of every query head in place and, for a layer that owns its
+//                     cache, norms the latent (x / rms * weight) and rotates the shared key part into the pages.
+//                     Angles are position * base^(-2i/dims), made in double so that they are exact to float32.
+//   latent_attention  one block per (token, group of heads): causal, optionally the last `window` keys only,
+//                     softmax in float32 kept online per warp and merged through shared memory; the result is the
+//                     attention-weighted latent times sigmoid(gate) of the head (the gate is a scalar per head, so it
+//                     commutes with the value up-projection that follows).
+#include "common.cuh"
+
+// Cache of one layer: page p holds plane 0 at p * page_elems, plane 1 at p * page_elems + page_size * rank.
+template <typename TA>
+__global__ void latent_prepare_kernel(TA* __restrict__ q, long long q_stride, const TA* __restrict__ dkv,
+                                      long long dkv_stride, const float* __restrict__ latent_norm_w,
+                                      const double* __restrict__ inv_freq, const int* __restrict__ positions,
+                                      const int* __restrict__ token_req, const int* __restrict__ table,
+                                      int table_width, TA* __restrict__ cache, int page_size, int n_heads, int dn,
+                                      int dr, int rot_dims, int rank, float eps) {
+  extern __shared__ float sm[];
+  float* cs = sm;                       // [rot_dims / 2] cosines, then as many sines
+  float* sn = sm + rot_dims / 2;
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rot_dims / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double s, c;
+    sincos((double)pos * inv_freq[i], &s, &c);
+    cs[i] = (float)c;
+    sn[i] = (float)s;
+  }
+  __syncthreads();
+  TA* qt = q + (size_t)t * q_stride;
+  for (int e = threadIdx.x; e < n_heads * half; e += blockDim.x) {
+    const int h = e / half, i = e % half;
+    TA* p = qt + (size_t)h * (dn + dr) + dn;
+    const float u = to_float(p[i]), v = to_float(p[i + half]);
+    p[i] = from_float<TA>(u * cs[i] - v * sn[i]);
+    p[i + half] = from_float<TA>(v * cs[i] + u * sn[i]);
+  }
+  if (dkv == nullptr) return;
+  const TA* row = dkv + (size_t)t * dkv_stride;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    const float x = to_float(row[c]);
+    ss += x * x;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)rank + eps);
+  int page = table[(size_t)token_req[t] * table_width + pos / page_size];
+  page = LLMRS_CHECKED_PAGE(page, 2, t);
+  const int slot = pos % page_size;
+  TA* pc = cache + (size_t)page * page_size * (rank + dr);
+  TA* c_out = pc + (size_t)slot * rank;
+  TA* r_out = pc + (size_t)page_size * rank + (size_t)slot * dr;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x)
+    c_out[c] = from_float<TA>(to_float(row[c]) * inv * latent_norm_w[c]);
+  const TA* kr = row + rank;
+  for (int i = threadIdx.x; i < dr; i += blockDim.x) {
+    float x;
+    if (i < half) x = to_float(kr[i]) * cs[i] - to_float(kr[i + half]) * sn[i];
+    else if (i < rot_dims) x = to_float(kr[i]) * cs[i - half] + to_float(kr[i - half]) * sn[i - half];
+    else x = to_float(kr[i]);
+    r_out[i] = from_float<TA>(x);
+  }
+}
+
+LLMRS_API int llmrs_latent_prepare(void* q, long long q_stride, const void* dkv, long long dkv_stride, int dtype,
+                                   const float* latent_norm_w, const double* inv_freq, const int* positions,
+                                   const int* token_req, const int* table, int table_width, void* cache,
+                                   int page_size, int n_tokens, int n_heads, int dn, int dr, int rot_dims, int rank,
+                                   float eps, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && n_heads > 0 && dn >= 0 && dr > 0 && rank > 0, "latent_prepare: bad sizes");
+  LLMRS_REQUIRE(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= dr, "latent_prepare: %d rotated dimensions of %d",
+                rot_dims, dr);
+  LLMRS_REQUIRE(dkv == nullptr || (cache && table && latent_norm_w), "latent_prepare: a cache write needs its pages");
+  if (n_tokens == 0) return 0;
+  const size_t smem = (size_t)rot_dims * sizeof(float);
+  if (dtype == LLMRS_F32)
+    latent_prepare_kernel<float><<<n_tokens, 128, smem, stream>>>(
+        (float*)q, q_stride, (const float*)dkv, dkv_stride, latent_norm_w, inv_freq, positions, token_req, table,
+        table_width, (float*)cache, page_size, n_heads, dn, dr, rot_dims, rank, eps);
+  else if (dtype == LLMRS_BF16)
+    latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>(
+        (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)dkv, dkv_stride, latent_norm_w, inv_freq, positions,
+        token_req, table, table_width, (__nv_bfloat16*)cache, page_size, n_heads, dn, dr, rot_dims, rank, eps);
+  else
+    return llmrs_fail("latent_prepare: unknown dtype %d", dtype);
+  return llmrs_launch_status("latent_prepare");
+}
+
+// ---------------------------------------------------------------------------------
+// The attention itself. HG heads per block share every cached row; a lane holds elements lane, lane + 32, ... of a row
+// (MAXC of them for the latent). Four warps take the keys in turn.
+// ---------------------------------------------------------------------------------
+constexpr int LA_WARPS = 4;
+
+template <typename TA, int HG, int MAXC>
+__global__ void __launch_bounds__(LA_WARPS * 32)
+latent_attention_kernel(const TA* __restrict__ qa, long long qa_token, long long qa_head,
+                        const TA* __restrict__ q, long long q_stride, int q_rot_at, int q_head_width,
+                        const TA* __restrict__ gate, long long gate_stride, const TA* __restrict__ cache,
+                        const int* __restrict__ table, int table_width, const int* __restrict__ positions,
+                        const int* __restrict__ token_req, TA* __restrict__ out, long long out_token,
+                        long long out_head, int n_heads, int rank, int dr, int page_size, int window, float scale) {
+  extern __shared__ float sm[];
+  float* s_qr = sm;                                        // [HG][dr]
+  float* s_m = s_qr + HG * dr;                             // [warps][HG]
+  float* s_l = s_m + LA_WARPS * HG;                        // [warps][HG]
+  float* s_acc = s_l + LA_WARPS * HG;                      // [warps][HG][rank]
+  const int t = blockIdx.x, h0 = blockIdx.y * HG;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = positions[t];
+  const int* tab = table + (size_t)token_req[t] * table_width;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+
+  float qv[HG][MAXC], acc[HG][MAXC], m[HG], l[HG];
+#pragma unroll
+  for (int g = 0; g < HG; ++g) {
+    const int h = min(h0 + g, n_heads - 1);
+    const TA* qrow = qa + (size_t)t * qa_token + (size_t)h * qa_head;
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * i;
+      qv[g][i] = c < rank ? to_float(qrow[c]) : 0.f;
+      acc[g][i] = 0.f;
+    }
+    m[g] = -INFINITY, l[g] = 0.f;
+    const TA* qr = q + (size_t)t * q_stride + (size_t)h * q_head_width + q_rot_at;
+    for (int i = threadIdx.x; i < dr; i += blockDim.x) s_qr[g * dr + i] = to_float(qr[i]);
+  }
+  __syncthreads();
+  const size_t page_elems = (size_t)page_size * (rank + dr);
+  for (int j = lo + warp; j <= pos; j += LA_WARPS) {
+    int page = tab[j / page_size];
+    page = LLMRS_CHECKED_PAGE(page, 3, j);
+    const int slot = j % page_size;
+    const TA* crow = cache + (size_t)page * page_elems + (size_t)slot * rank;
+    const TA* rrow = cache + (size_t)page * page_elems + (size_t)page_size * rank + (size_t)slot * dr;
+    float cv[MAXC];
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * i;
+      cv[i] = c < rank ? to_float(crow[c]) : 0.f;
+    }
+    float part[HG];
+#pragma unroll
+    for (int g = 0; g < HG; ++g) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXC; ++i) s = fmaf(qv[g][i], cv[i], s);
+      part[g] = s;
+    }
+    for (int i = lane; i < dr; i += 32) {
+      const float kv = to_float(rrow[i]);
+#pragma unroll
+      for (int g = 0; g < HG; ++g) part[g] = fmaf(s_qr[g * dr + i], kv, part[g]);
+    }
+#pragma unroll
+    for (int g = 0; g < HG; ++g) {
+      const float s = warp_sum(part[g]) * scale;
+      const float m_new = fmaxf(m[g], s);
+      const float corr = expf(m[g] - m_new);       // exp(-inf) = 0 at the first key
+      const float p = expf(s - m_new);
+      l[g] = l[g] * corr + p;
+      m[g] = m_new;
+#pragma unroll
+      for (int i = 0; i < MAXC; ++i) acc[g][i] = fmaf(p, cv[i], acc[g][i] * corr);
+    }
+  }
+  // Merge the warps' partial softmaxes.
+#pragma unroll
+  for (int g = 0; g < HG; ++g) {
+    if (lane == 0) s_m[warp * HG + g] = m[g], s_l[warp * HG + g] = l[g];
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * i;
+      if (c < rank) s_acc[(size_t)(warp * HG + g) * rank + c] = acc[g][i];
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < HG * rank; e += blockDim.x) {
+    const int g = e / rank, c = e % rank;
+    if (h0 + g >= n_heads) continue;
+    float mm = -INFINITY;
+    for (int w = 0; w < LA_WARPS; ++w) mm = fmaxf(mm, s_m[w * HG + g]);
+    float num = 0.f, den = 0.f;
+    for (int w = 0; w < LA_WARPS; ++w) {
+      const float mw = s_m[w * HG + g];
+      if (mw == -INFINITY) continue;                // a warp that saw no key
+      const float f = expf(mw - mm);
+      num = fmaf(f, s_acc[(size_t)(w * HG + g) * rank + c], num);
+      den = fmaf(f, s_l[w * HG + g], den);
+    }
+    const float gt = 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + h0 + g])));
+    out[(size_t)t * out_token + (size_t)(h0 + g) * out_head + c] = from_float<TA>(num / den * gt);
+  }
+}
+
+template <typename TA, int HG>
+static int launch_latent(int maxc, dim3 grid, size_t smem, cudaStream_t stream, const void* qa, long long qa_token,
+                         long long qa_head, const void* q, long long q_stride, int q_rot_at, int q_head_width,
+                         const void* gate, long long gate_stride, const void* cache, const int* table,
+                         int table_width, const int* positions, const int* token_req, void* out, long long out_token,
+                         long long out_head, int n_heads, int rank, int dr, int page_size, int window, float scale) {
+#define LLMRS_LA(C)                                                                                                \
+  latent_attention_kernel<TA, HG, C><<<grid, LA_WARPS * 32, smem, stream>>>(                                       \
+      (const TA*)qa, qa_token, qa_head, (const TA*)q, q_stride, q_rot_at, q_head_width, (const TA*)gate,           \
+      gate_stride, (const TA*)cache, table, table_width, positions, token_req, (TA*)out, out_token, out_head,      \
+      n_heads, rank, dr, page_size, window, scale)
+  if (maxc <= 2) LLMRS_LA(2);
+  else if (maxc <= 4) LLMRS_LA(4);
+  else if (maxc <= 8) LLMRS_LA(8);
+  else LLMRS_LA(16);
+#undef LLMRS_LA
+  return llmrs_launch_status("latent_attention");
+}
+
+// qa: folded queries [tokens, heads, rank] with strides; q: the projected queries, head h's rotated part at
+// q + t * q_stride + h * q_head_width + q_rot_at; gate: raw gate values [tokens, heads] (row stride given);
+// out: [tokens, heads, rank] with strides.
+LLMRS_API int llmrs_latent_attention(const void* qa, long long qa_token, long long qa_head, const void* q,
+                                     long long q_stride, int q_rot_at, int q_head_width, const void* gate,
+                                     long long gate_stride, const void* cache, int dtype, const int* table,
+                                     int table_width, const int* positions, const int* token_req, void* out,
+                                     long long out_token, long long out_head, int n_tokens, int n_heads, int rank,
+                                     int dr, int page_size, int window, float scale, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && n_heads > 0 && rank > 0 && dr > 0 && page_size > 0, "latent_attention: bad sizes");
+  LLMRS_REQUIRE(rank <= 512, "latent_attention: a latent of at most 512, got %d", rank);
+  LLMRS_REQUIRE(window >= 0, "latent_attention: bad window");
+  if (n_tokens == 0) return 0;
+  const int hg = n_heads >= 4 ? 4 : 1;
+  const int maxc = (rank + 31) / 32;
+  const size_t smem = ((size_t)hg * dr + 2 * LA_WARPS * hg + (size_t)LA_WARPS * hg * rank) * sizeof(float);
+  LLMRS_REQUIRE(smem <= 48 * 1024, "latent_attention: sizes need %zu bytes of shared memory", smem);
+  dim3 grid(n_tokens, (n_heads + hg - 1) / hg);
+  LLMRS_REQUIRE(grid.y <= 65535, "latent_attention: too many heads");
+#define LLMRS_LA_ARGS                                                                                              \
+  maxc, grid, smem, stream, qa, qa_token, qa_head, q, q_stride, q_rot_at, q_head_width, gate, gate_stride, cache,  \
+      table, table_width, positions, token_req, out, out_token, out_head, n_heads, rank, dr, page_size, window, scale
+  if (dtype == LLMRS_F32) return hg == 4 ? launch_latent<float, 4>(LLMRS_LA_ARGS) : launch_latent<float, 1>(LLMRS_LA_ARGS);
+  if (dtype == LLMRS_BF16)
+    return hg == 4 ? launch_latent<__nv_bfloat16, 4>(LLMRS_LA_ARGS) : launch_latent<__nv_bfloat16, 1>(LLMRS_LA_ARGS);
+#undef LLMRS_LA_ARGS
+  return llmrs_fail("latent_attention: unknown dtype %d", dtype);
+}

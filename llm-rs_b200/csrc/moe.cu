@@ -1,0 +1,155 @@
+// Routing and grouping for mixtures of experts.
+//
+// A router fills, per assignment a = token * top + k, the expert it names and its weight. The sort kernel then
+// orders the assignments by expert (a counting sort that keeps token order inside an expert), cuts every expert's
+// run into tiles of rows for the grouped matrix product (gemm_grouped.cu) and tells each assignment where its row
+// went; the combine kernel sums a token's rows in the order of k with their weights, in float32. Everything stays on
+// the device, so steps replay from CUDA graphs.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------
+// Router "table": token id -> a row of `top` expert ids, every expert weighted 1 / top.
+// ---------------------------------------------------------------------------------
+__global__ void moe_route_table_kernel(const int* __restrict__ token_ids, const int* __restrict__ table,
+                                       int* __restrict__ expert_of, float* __restrict__ weight_of, int n_assign,
+                                       int top, int vocab, int n_experts) {
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a >= n_assign) return;
+  int id = token_ids[a / top];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  int e = table[(size_t)id * top + a % top];
+  e = e < 0 ? 0 : (e >= n_experts ? n_experts - 1 : e);
+  expert_of[a] = e;
+  weight_of[a] = 1.0f / (float)top;
+}
+
+LLMRS_API int llmrs_moe_route_table(const int* token_ids, const int* table, int* expert_of, float* weight_of,
+                                    int n_tokens, int top, int vocab, int n_experts, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && top > 0 && vocab > 0 && n_experts > 0, "moe_route_table: bad sizes");
+  const int n = n_tokens * top;
+  if (n == 0) return 0;
+  moe_route_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(token_ids, table, expert_of, weight_of, n, top, vocab,
+                                                             n_experts);
+  return llmrs_launch_status("moe_route_table");
+}
+
+// ---------------------------------------------------------------------------------
+// Counting sort of the assignments by expert, one block. Warp w owns a contiguous run of assignments; inside a
+// warp's batch of 32 the lanes that name the same expert find their order with match_any. counts[w][e] first holds
+// what warp w has seen of expert e, then (after the scan over w) where warp w's rows of expert e begin.
+//   row_of[a]     sorted row of assignment a
+//   src_token[r]  token whose activations sorted row r reads
+//   tiles[i]      (expert, first row, rows) for the grouped product, rows <= tile_rows; *n_tiles of them
+// ---------------------------------------------------------------------------------
+constexpr int MOE_SORT_THREADS = 1024, MOE_SORT_WARPS = MOE_SORT_THREADS / 32;
+
+__global__ void __launch_bounds__(MOE_SORT_THREADS)
+moe_sort_kernel(const int* __restrict__ expert_of, int* __restrict__ row_of, int* __restrict__ src_token,
+                int* __restrict__ tiles, int* __restrict__ n_tiles, int n_assign, int top, int n_experts,
+                int tile_rows) {
+  extern __shared__ int sm[];
+  int* counts = sm;                                   // [warps][experts]
+  int* start = sm + MOE_SORT_WARPS * n_experts;       // [experts + 1]
+  int* tile_at = start + n_experts + 1;               // [experts + 1]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < MOE_SORT_WARPS * n_experts; i += MOE_SORT_THREADS) counts[i] = 0;
+  __syncthreads();
+  const int per_warp = ((n_assign + MOE_SORT_WARPS - 1) / MOE_SORT_WARPS + 31) / 32 * 32;
+  const int lo = warp * per_warp, hi = min(n_assign, lo + per_warp);
+  int* mine = counts + warp * n_experts;
+  for (int base = lo; base < hi; base += 32) {
+    const int a = base + lane;
+    const bool live = a < hi;
+    const int e = live ? expert_of[a] : -1 - lane;    // idle lanes match nobody
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int before = __popc(peers & ((1u << lane) - 1u));
+    int seen = 0;
+    if (live) seen = mine[e];
+    __syncwarp();
+    if (live) {
+      row_of[a] = seen + before;                      // order inside (warp, expert); completed below
+      if (before == 0) mine[e] = seen + __popc(peers);
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = tid; e < n_experts; e += MOE_SORT_THREADS) {
+    int total = 0;
+    for (int w = 0; w < MOE_SORT_WARPS; ++w) {
+      const int c = counts[w * n_experts + e];
+      counts[w * n_experts + e] = total;
+      total += c;
+    }
+    start[e + 1] = total;                             // for now: the expert's number of rows
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int rows = 0, t = 0;
+    start[0] = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      const int c = start[e + 1];
+      tile_at[e] = t;
+      t += (c + tile_rows - 1) / tile_rows;
+      rows += c;
+      start[e + 1] = rows;
+    }
+    tile_at[n_experts] = t;
+    *n_tiles = t;
+  }
+  __syncthreads();
+  for (int e = tid; e < n_experts; e += MOE_SORT_THREADS) {
+    const int first = start[e], c = start[e + 1] - first;
+    for (int i = 0, t = tile_at[e]; i < c; i += tile_rows, ++t) {
+      tiles[3 * t] = e;
+      tiles[3 * t + 1] = first + i;
+      tiles[3 * t + 2] = min(tile_rows, c - i);
+    }
+  }
+  for (int a = lo + lane; a < hi; a += 32) {
+    const int e = expert_of[a];
+    const int row = start[e] + mine[e] + row_of[a];
+    row_of[a] = row;
+    src_token[row] = a / top;
+  }
+}
+
+LLMRS_API int llmrs_moe_sort(const int* expert_of, int* row_of, int* src_token, int* tiles, int* n_tiles,
+                             int n_assign, int top, int n_experts, int tile_rows, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_assign >= 0 && top > 0 && tile_rows > 0, "moe_sort: bad sizes");
+  LLMRS_REQUIRE(n_experts > 0 && n_experts <= 256, "moe_sort: 1 to 256 experts, got %d", n_experts);
+  if (n_assign == 0) return 0;
+  const size_t smem = ((size_t)MOE_SORT_WARPS * n_experts + 2 * (n_experts + 1)) * sizeof(int);
+  moe_sort_kernel<<<1, MOE_SORT_THREADS, smem, stream>>>(expert_of, row_of, src_token, tiles, n_tiles, n_assign, top,
+                                                         n_experts, tile_rows);
+  return llmrs_launch_status("moe_sort");
+}
+
+// ---------------------------------------------------------------------------------
+// out[t, :] = sum_k weight_of[t * top + k] * rows[row_of[t * top + k], :], k in order, float32.
+// ---------------------------------------------------------------------------------
+template <typename TO>
+__global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ row_of,
+                                   const float* __restrict__ weight_of, TO* __restrict__ out, int top, int width) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < top; ++k)
+      s = fmaf(weight_of[t * top + k], rows[(size_t)row_of[t * top + k] * width + c], s);
+    out[(size_t)t * width + c] = from_float<TO>(s);
+  }
+}
+
+LLMRS_API int llmrs_moe_combine(const float* rows, const int* row_of, const float* weight_of, void* out,
+                                int out_dtype, int n_tokens, int top, int width, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && top > 0 && width > 0, "moe_combine: bad sizes");
+  if (n_tokens == 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (out_dtype == LLMRS_F32)
+    moe_combine_kernel<float><<<n_tokens, threads, 0, stream>>>(rows, row_of, weight_of, (float*)out, top, width);
+  else if (out_dtype == LLMRS_BF16)
+    moe_combine_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(rows, row_of, weight_of,
+                                                                        (__nv_bfloat16*)out, top, width);
+  else
+    return llmrs_fail("moe_combine: unknown dtype %d", out_dtype);
+  return llmrs_launch_status("moe_combine");
+}

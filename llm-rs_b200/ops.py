@@ -659,3 +659,214 @@ def check_attention_error() -> None:
         fn.restype = ctypes.c_int
         if fn() > 0:
             raise KernelError(f"an attention kernel gave up waiting on a barrier ({name}); its output is invalid")
+
+
+# -- blocks that norm a branch's output; token shift; soft cap ---------------------------------------
+_LL = ctypes.c_longlong
+
+
+def token_shift(x: torch.Tensor, mu: Optional[torch.Tensor], state: Optional[torch.Tensor], ctx,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """``y_t = x_t + (x_{t-1} - x_t) * mu`` over the float32 rows ``x`` of a step, rounded to ``out_dtype``. The row
+    before a request's first token of the step comes from ``state[slot]`` (zeros after admission), which then takes
+    the request's last row of the step. ``mu`` None: a plain conversion of ``x``."""
+    _need(x, "x", torch.float32)
+    n, width = x.shape
+    out = torch.empty((n, width), dtype=out_dtype, device=x.device)
+    if mu is not None:
+        _need(mu, "mu", torch.float32)
+        _need(state, "state", torch.float32)
+        if mu.numel() != width or state.size(-1) != width:
+            raise KernelError(f"token shift of width {width}: mu has {mu.numel()}, state rows {state.size(-1)}")
+        args = (_ptr(ctx.token_req), _ptr(ctx.q_start), _ptr(ctx.n_new), _ptr(ctx.slot_ids))
+    else:
+        args = (None, None, None, None)
+    _check(_lib().llmrs_token_shift(_ptr(x), _ptr(mu), _ptr(state), *args, _ptr(out), dtype_code(out_dtype), n, width,
+                                    _stream()), "token_shift")
+    return out
+
+
+def outnorm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``h += y / sqrt(mean(y^2) + eps) * weight`` row by row, in float32, in place."""
+    _need(h, "h", torch.float32)
+    _need(y, "y")
+    _need(weight, "weight", torch.float32)
+    if y.shape != h.shape or weight.numel() != h.size(-1):
+        raise KernelError(f"outnorm_add: h {tuple(h.shape)}, y {tuple(y.shape)}, weight {weight.numel()}")
+    _check(_lib().llmrs_outnorm_add(_ptr(h), _ptr(y), dtype_code(y.dtype), _ptr(weight), h.size(0), h.size(1),
+                                    ctypes.c_float(eps), _stream()), "outnorm_add")
+    return h
+
+
+def softcap_(z: torch.Tensor, cap: float) -> torch.Tensor:
+    """``z = cap * tanh(z / cap)`` in place (float32)."""
+    _need(z, "z", torch.float32)
+    _check(_lib().llmrs_softcap(_ptr(z), _LL(z.numel()), ctypes.c_float(cap), _stream()), "softcap")
+    return z
+
+
+def tanh_slice(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``tanh`` of a 2-D view with dense rows (a column slice of a wider product), as a contiguous tensor."""
+    _need(x, "x", contiguous=False)
+    out = torch.empty(tuple(x.shape), dtype=out_dtype, device=x.device)
+    _check(_lib().llmrs_tanh_slice(_ptr(x), dtype_code(x.dtype), _LL(_row_stride(x, "x")), _ptr(out),
+                                   dtype_code(out_dtype), x.size(0), x.size(1), _stream()), "tanh_slice")
+    return out
+
+
+# -- many small products in one launch ----------------------------------------------------------------
+GROUPED_TILE_ROWS = 64
+
+
+def _strides3(t: torch.Tensor, name: str):
+    """(row stride, batch stride) of a [rows, batches, cols] view with dense columns."""
+    if t.dim() != 3 or (t.size(2) > 1 and t.stride(2) != 1):
+        raise KernelError(f"{name} must be [rows, batches, cols] with dense columns, got {tuple(t.shape)} {t.stride()}")
+    return t.stride(0), t.stride(1)
+
+
+def gemm_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, round_x: bool = False) -> torch.Tensor:
+    """``out[m, b, :] = w[b] @ x[m, b, :]`` for x [M, B, K] and out [M, B, N] (any row and batch strides) and
+    w [B, N, K] contiguous: the heads of a tensor as batches, without a copy. float32 accumulation on the CUDA
+    cores in a fixed order over k."""
+    _need(x, "x", contiguous=False)
+    _need(w, "w")
+    _need(out, "out", contiguous=False)
+    M, B, K = x.shape
+    if w.dim() != 3 or w.size(0) != B or w.size(2) != K or out.shape != (M, B, w.size(1)):
+        raise KernelError(f"gemm_batched: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    xs, xb = _strides3(x, "x")
+    os_, ob = _strides3(out, "out")
+    N = w.size(1)
+    _check(_lib().llmrs_gemm_grouped(
+        _ptr(x), dtype_code(x.dtype), _LL(xs), _LL(xb), _ptr(w), None, dtype_code(w.dtype), _LL(N * K), _ptr(out),
+        dtype_code(out.dtype), _LL(os_), _LL(ob), M, N, K, B, None, None, 0, None, int(round_x), ctypes.c_float(0),
+        ctypes.c_float(0), ctypes.c_float(0), _stream()), "gemm_batched")
+    return out
+
+
+def gemm_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor,
+                 src: Optional[torch.Tensor], w2: Optional[torch.Tensor] = None, round_x: bool = False,
+                 limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0) -> torch.Tensor:
+    """Rows sorted by group against each group's own weights: ``out[r] = w[g(r)] @ x[src[r]]`` for the rows of every
+    tile (``tiles`` [max, 3] = group, first row, rows; ``n_tiles`` on the device; from ``moe_sort``). With ``w2`` the
+    gated unit ``g * sigmoid(alpha * g) * (u + shift)``, g = min(w x, limit), u = clamp(w2 x, -limit, limit)."""
+    _need(x, "x", contiguous=False)
+    _need(w, "w")
+    _need(out, "out")
+    _need(tiles, "tiles", torch.int32)
+    _need(n_tiles, "n_tiles", torch.int32)
+    G, N, K = w.shape
+    if x.size(1) != K or out.size(1) != N or (w2 is not None and w2.shape != w.shape):
+        raise KernelError(f"gemm_grouped: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if src is not None:
+        _need(src, "src", torch.int32)
+    _check(_lib().llmrs_gemm_grouped(
+        _ptr(x), dtype_code(x.dtype), _LL(_row_stride(x, "x")), _LL(0), _ptr(w), _ptr(w2), dtype_code(w.dtype),
+        _LL(N * K), _ptr(out), dtype_code(out.dtype), _LL(out.stride(0)), _LL(0), out.size(0), N, K, 0, _ptr(tiles),
+        _ptr(n_tiles), tiles.size(0), _ptr(src), int(round_x), ctypes.c_float(limit), ctypes.c_float(alpha),
+        ctypes.c_float(shift), _stream()), "gemm_grouped")
+    return out
+
+
+# -- mixtures of experts --------------------------------------------------------------------------------
+def moe_route_table(token_ids: torch.Tensor, table: torch.Tensor, n_experts: int):
+    """Routing by token id: ``table`` [vocab, top] int32 names each id's experts, all weighted 1/top. Returns
+    (expert_of int32 [tokens * top], weight_of float32 [tokens * top])."""
+    _need(token_ids, "token_ids", torch.int32)
+    _need(table, "table", torch.int32)
+    vocab, top = table.shape
+    n = token_ids.numel()
+    expert_of = torch.empty((n * top,), dtype=torch.int32, device=table.device)
+    weight_of = torch.empty((n * top,), dtype=torch.float32, device=table.device)
+    _check(_lib().llmrs_moe_route_table(_ptr(token_ids), _ptr(table), _ptr(expert_of), _ptr(weight_of), n, top, vocab,
+                                        n_experts, _stream()), "moe_route_table")
+    return expert_of, weight_of
+
+
+def moe_sort(expert_of: torch.Tensor, top: int, n_experts: int):
+    """Order the assignments by expert. Returns (row_of [assignments], src_token [assignments], tiles [max, 3],
+    n_tiles [1]): see ``gemm_grouped``."""
+    _need(expert_of, "expert_of", torch.int32)
+    n = expert_of.numel()
+    dev = expert_of.device
+    row_of = torch.empty((n,), dtype=torch.int32, device=dev)
+    src_token = torch.empty((n,), dtype=torch.int32, device=dev)
+    max_tiles = -(-n // GROUPED_TILE_ROWS) + n_experts
+    tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=dev)
+    n_tiles = torch.empty((1,), dtype=torch.int32, device=dev)
+    _check(_lib().llmrs_moe_sort(_ptr(expert_of), _ptr(row_of), _ptr(src_token), _ptr(tiles), _ptr(n_tiles), n, top,
+                                 n_experts, GROUPED_TILE_ROWS, _stream()), "moe_sort")
+    return row_of, src_token, tiles, n_tiles
+
+
+def moe_combine(rows: torch.Tensor, row_of: torch.Tensor, weight_of: torch.Tensor, top: int,
+                out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``out[t] = sum_k weight_of[t, k] * rows[row_of[t, k]]`` in float32, k in order."""
+    _need(rows, "rows", torch.float32)
+    n = row_of.numel() // top
+    out = torch.empty((n, rows.size(1)), dtype=out_dtype, device=rows.device)
+    _check(_lib().llmrs_moe_combine(_ptr(rows), _ptr(row_of), _ptr(weight_of), _ptr(out), dtype_code(out_dtype), n, top,
+                                    rows.size(1), _stream()), "moe_combine")
+    return out
+
+
+# -- the generalized delta rule -------------------------------------------------------------------------
+def delta_rule(r, k, v, gate, a_raw, decay_raw, decay_bias, a_bias, norm_w, state, ctx, n_heads: int, d: int,
+               decay_scale: float, key_eps: float, norm_eps: float) -> torch.Tensor:
+    """The recurrence of ``csrc/delta_rule.cu`` over a step's tokens. r, k, v, gate, a_raw: column slices
+    [tokens, heads * d] of one product (equal row strides); decay_raw float32 [tokens, heads * d] contiguous;
+    state float32 [slots, heads, d, d], updated in place. Returns [tokens, heads * d] in the activation type."""
+    stride = _row_stride(r, "r")
+    for name, t in (("k", k), ("v", v), ("gate", gate), ("a_raw", a_raw)):
+        _need(t, name, r.dtype, contiguous=False)
+        if _row_stride(t, name) != stride:
+            raise KernelError("delta_rule: the slices must share their row stride")
+    _need(decay_raw, "decay_raw", torch.float32)
+    _need(state, "state", torch.float32)
+    out = torch.empty((r.size(0), n_heads * d), dtype=r.dtype, device=r.device)
+    _check(_lib().llmrs_delta_rule(
+        _ptr(r), _ptr(k), _ptr(v), _ptr(gate), _ptr(a_raw), _LL(stride), dtype_code(r.dtype), _ptr(decay_raw),
+        _ptr(decay_bias), _ptr(a_bias), _ptr(norm_w), _ptr(state), _ptr(ctx.q_start), _ptr(ctx.n_new),
+        _ptr(ctx.slot_ids), _ptr(out), ctx.n_requests, n_heads, d, ctypes.c_float(decay_scale),
+        ctypes.c_float(key_eps), ctypes.c_float(norm_eps), _stream()), "delta_rule")
+    return out
+
+
+# -- latent attention -----------------------------------------------------------------------------------
+def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], latent_norm_w, inv_freq: torch.Tensor, ctx, table,
+                   cache: Optional[torch.Tensor], page_size: int, n_heads: int, dn: int, dr: int, rot_dims: int,
+                   rank: int, eps: float) -> None:
+    """Rotate the rot part of every query head of ``q`` ([tokens, heads * (dn + dr)] view) in place; with ``dkv``
+    ([tokens, rank + dr] view) also norm the latent and rotate the shared key part into the pages ``cache``
+    ([pages, 1, page_size * (rank + dr)])."""
+    _need(q, "q", contiguous=False)
+    _need(inv_freq, "inv_freq", torch.float64)
+    if dkv is not None:
+        _need(dkv, "dkv", q.dtype, contiguous=False)
+        _need(cache, "cache", q.dtype)
+    _check(_lib().llmrs_latent_prepare(
+        _ptr(q), _LL(_row_stride(q, "q")), _ptr(dkv), _LL(0 if dkv is None else _row_stride(dkv, "dkv")),
+        dtype_code(q.dtype), _ptr(latent_norm_w), _ptr(inv_freq), _ptr(ctx.positions), _ptr(ctx.token_req),
+        _ptr(table), 0 if table is None else table.size(1), _ptr(cache), page_size, q.size(0), n_heads, dn, dr,
+        rot_dims, rank, ctypes.c_float(eps), _stream()), "latent_prepare")
+
+
+def latent_attention(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cache: torch.Tensor, table, ctx,
+                     out: torch.Tensor, n_heads: int, dn: int, dr: int, rank: int, page_size: int, window: int,
+                     scale: float) -> torch.Tensor:
+    """Attention over cached latent rows with folded queries ``qa`` [tokens, heads, rank]; ``q`` the rotated
+    projected queries, ``gate`` the raw per-head gates [tokens, heads]; ``out`` [tokens, heads, rank] (any strides)."""
+    _need(qa, "qa", contiguous=False)
+    _need(q, "q", qa.dtype, contiguous=False)
+    _need(gate, "gate", qa.dtype, contiguous=False)
+    _need(cache, "cache", qa.dtype)
+    _need(out, "out", qa.dtype, contiguous=False)
+    qs, qh = _strides3(qa, "qa")
+    os_, oh = _strides3(out, "out")
+    _check(_lib().llmrs_latent_attention(
+        _ptr(qa), _LL(qs), _LL(qh), _ptr(q), _LL(_row_stride(q, "q")), dn, dn + dr, _ptr(gate),
+        _LL(_row_stride(gate, "gate")), _ptr(cache), dtype_code(qa.dtype), _ptr(table), table.size(1),
+        _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(out), _LL(os_), _LL(oh), qa.size(0), n_heads, rank, dr,
+        page_size, window, ctypes.c_float(scale), _stream()), "latent_attention")
+    return out

@@ -3,9 +3,12 @@ from __future__ import annotations
 
 import os
 
-from .base import Block, PreNormed, Runtime
+import torch
+
+from .. import ops
+from .base import Block, Part, PreNormed, Runtime
 from .registry import build, register
-from .spec import LayerSpec
+from .spec import LayerSpec, StateNeed, WeightSpec
 
 
 # Steps of few tokens spread each norm over the products around it (see ``PreNormed``); LLMRS_LINK_NORMS=0
@@ -65,3 +68,74 @@ class PreNormBlock(Block):
         if fused:
             return h, self.feed_forward.forward(y, ctx, residual=h)
         return h, self.feed_forward.forward(y, ctx)
+
+
+class TokenShift(Part):
+    """``y_t = x_t + (x_{t-1} - x_t) * mu``: what a mixer reads is mixed, channel by channel, with the previous
+    token's row as it was before the mixing (zeros before a sequence's first token). The last row of a step is kept
+    per request as fixed-size state, so a sequence may be cut anywhere. ``name`` is mu's tensor after the prefix."""
+    STATE = "shift.previous"
+
+    def __init__(self, dim: int, name: str = "shift", prefix: str = ""):
+        self.dim, self.name = dim, prefix + name
+
+    def weight_specs(self):
+        return [WeightSpec(self.name, (self.dim,), role="bias")]
+
+    def bind(self, tensors, runtime: Runtime):
+        self.mu = tensors[self.name].to(torch.float32).contiguous()
+        self.act_dtype = runtime.act_dtype
+
+    def state_need(self) -> StateNeed:
+        return StateNeed({self.STATE: (self.dim,)})
+
+    def forward(self, h, ctx, cache):
+        return ops.token_shift(h, self.mu, cache.state[self.STATE], ctx, self.act_dtype)
+
+
+@register("block", "outnorm")
+class OutNormBlock(Block):
+    """``h += norm1(mixer(shift(h))); h += norm2(feed_forward(h))``: the branches read the residual stream itself
+    (rounded to the activation type) and the norms sit on their OUTPUTS. ``token_shift`` (the name of its tensor,
+    or "") puts a ``TokenShift`` before the mixer; a layer may have no feed-forward. The residual sums and the
+    norms' statistics are float32."""
+
+    def __init__(self, layer: LayerSpec, token_shift: str = "", prefix: str = ""):
+        p = layer.prefix
+        self.mixer_norm = build("norm", layer.mixer_norm, prefix=p)
+        self.mixer = build("mixer", layer.mixer, prefix=p + layer.mixer_scope)
+        self.shift = TokenShift(self.mixer_norm.dim, token_shift, prefix=p) if token_shift else None
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = build("norm", layer.feed_forward_norm, prefix=p)
+            self.feed_forward = build("feed_forward", layer.feed_forward, prefix=p + layer.feed_forward_scope)
+
+    def parts(self):
+        return [p for p in (self.shift, self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm)
+                if p is not None]
+
+    def chain(self):
+        return []
+
+    def weight_specs(self):
+        return [s for part in self.parts() for s in part.weight_specs()]
+
+    def bind(self, tensors, runtime: Runtime):
+        self.act_dtype = runtime.act_dtype
+        for part in self.parts():
+            part.bind(tensors, runtime)
+
+    def state_need(self):
+        return self.shift.state_need() if self.shift is not None else None
+
+    def forward(self, h, pending, ctx, cache):
+        if pending is not None:      # a block before this one left its last branch unadded
+            ops.residual_add(h, pending)
+        x = self.shift.forward(h, ctx, cache) if self.shift is not None else ops.token_shift(
+            h, None, None, ctx, self.act_dtype)
+        self.mixer_norm.add_normed(h, self.mixer.forward(x, ctx, cache))
+        if self.feed_forward is not None:
+            x = h if getattr(self.feed_forward, "reads_residual", False) else ops.token_shift(
+                h, None, None, ctx, self.act_dtype)
+            self.feed_forward_norm.add_normed(h, self.feed_forward.forward(x, ctx))
+        return h, None

@@ -34,11 +34,11 @@ class LinearHead(Part):
     (llm-core/src/graph/builder.rs:408-437). ``tied_to`` names the embedding table that
     serves as W when the model ties them (llm-core/src/backends/weights.rs:144-157): one
     buffer, used by both. A tied model's folder may still store the head's matrix (a copy of the
-    table); it is accepted and not read."""
+    table); it is accepted and not read. ``softcap`` > 0: ``logits = softcap * tanh(logits / softcap)``."""
 
     def __init__(self, vocab_size: int, hidden_size: int, name: str = "head.weight", tied_to: str = "",
-                 prefix: str = ""):
-        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+                 softcap: float = 0.0, prefix: str = ""):
+        self.vocab_size, self.hidden_size, self.softcap = vocab_size, hidden_size, float(softcap)
         self.name, self.tied_to = prefix + name, tied_to
 
     def weight_specs(self):
@@ -53,4 +53,5 @@ class LinearHead(Part):
         return [self.proj]
 
     def forward(self, x):
-        return self.proj.forward(x, out_dtype=torch.float32)
+        logits = self.proj.forward(x, out_dtype=torch.float32)
+        return ops.softcap_(logits, self.softcap) if self.softcap > 0 else logits

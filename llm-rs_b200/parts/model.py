@@ -43,15 +43,21 @@ class DecoderModel:
             lin.next_weight = after.weight if lin.warms_next and after.weight.dtype == torch.bfloat16 else None
 
     def cache_needs(self) -> List[Tuple[Optional[CacheNeed], Optional[StateNeed]]]:
-        """Per run-order entry: the pages and the state its mixer wants. An entry that
-        reads another entry's cache wants nothing of its own."""
+        """Per run-order entry: the pages and the state its mixer wants, plus the state its block wants for itself.
+        An entry that reads another entry's cache wants no pages and no mixer state of its own (it sees the other
+        entry's), but keeps its block's state."""
         needs = []
         for step in self.spec.run_order:
+            block = self.blocks[step.layer]
+            own = getattr(block, "state_need", lambda: None)()       # state of the block itself (a token shift)
             if step.cache_of is not None:
-                needs.append((None, None))
+                needs.append((None, own))
             else:
-                mixer = self.blocks[step.layer].mixer
-                needs.append((mixer.cache_need(), mixer.state_need()))
+                mixer = block.mixer
+                state = mixer.state_need()
+                if own is not None:
+                    state = StateNeed({**(state.tensors if state is not None else {}), **own.tensors})
+                needs.append((mixer.cache_need(), state))
         return needs
 
     def forward(self, ctx) -> Optional[torch.Tensor]:

@@ -15,22 +15,31 @@ from .spec import WeightSpec
 class RMSNorm(Norm):
     """``y = x / sqrt(mean(x^2) + eps) * w`` with float32 statistics and a plain weight
     (llm-core/src/backends/attention.rs:55-68,98-104). ``dim`` and ``eps`` are parameters;
-    ``name`` is the weight's name after the prefix."""
+    ``name`` is the weight's name after the prefix. With ``offset`` the stored weight lies around zero and the
+    factor is ``offset + w`` (added once at load, in float32).
 
-    def __init__(self, dim: int, eps: float, name: str = "weight", prefix: str = ""):
+    ``add_normed(h, y)`` is the norm of a block that norms a branch's OUTPUT: ``h += norm(y)``."""
+
+    def __init__(self, dim: int, eps: float, name: str = "weight", offset: float = 0.0, prefix: str = ""):
         self.dim, self.eps, self.prefix, self.name = dim, float(eps), prefix, name
+        self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
         self.act_dtype = None
 
     def weight_specs(self):
-        return [WeightSpec(self.prefix + self.name, (self.dim,), role="norm")]
+        return [WeightSpec(self.prefix + self.name, (self.dim,), role="norm_offset" if self.offset else "norm")]
 
     def bind(self, tensors, runtime: Runtime):
         self.weight = tensors[self.prefix + self.name].to(torch.float32).contiguous()
+        if self.offset:
+            self.weight = self.weight + self.offset
         self.act_dtype = runtime.act_dtype
 
     def forward(self, h, delta, rows=None):
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self.act_dtype, rows=rows)
+
+    def add_normed(self, h, y):
+        return ops.outnorm_add(h, y, self.weight, self.eps)
 
     def link(self):
         return (self.weight, self.eps) if self.act_dtype == torch.bfloat16 else None

@@ -31,7 +31,7 @@ class LayerSpec:
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]               # None: the layer has no feed-forward
     mixer_norm: PartSpec
     feed_forward_norm: Optional[PartSpec] = None     # a block with one norm for both branches has none
     mixer_scope: str = ""
@@ -82,8 +82,10 @@ class WeightSpec:
       "matrix"     ~N(0, sigma); kept in the stored floating type (bfloat16 or float32)
       "embedding"  like "matrix"
       "norm"       1 + N(0, norm_jitter); held as float32 (exact from bfloat16)
+      "norm_offset" N(0, norm_jitter): a norm weight stored around zero; held as float32
       "bias"       ~N(0, sigma)
       "int_table"  integers, held as int32
+      "expert_table" int32 rows of different integers below ``limit`` (which experts a row uses)
     ``optional`` tensors may be absent from the folder. ``load=False`` marks a tensor that the folder
     may hold but the part does not use (a stored copy of a tied matrix): its shape is checked, it is
     not read, and the random-weights mode does not write it.
@@ -93,6 +95,7 @@ class WeightSpec:
     role: str = "matrix"
     optional: bool = False
     load: bool = True
+    limit: int = 0
 
 
 @dataclass(frozen=True)

@@ -21,10 +21,16 @@ from .safetensors_io import save_file
 def _make(spec: WeightSpec, seed: int, index: int, sigma: float, norm_jitter: float, dtype: torch.dtype, device):
     gen = torch.Generator(device=device)
     gen.manual_seed((seed * 1_000_003 + index) & 0x7FFFFFFFFFFFFFFF)
+    if spec.role == "expert_table":
+        # Every row names ``shape[1]`` different experts out of ``spec.limit``.
+        order = torch.rand((spec.shape[0], spec.limit), generator=gen, device=device).argsort(dim=1)
+        return order[:, : spec.shape[1]].to(torch.int32).contiguous()
     if spec.role == "int_table":
         return torch.randint(0, 2**15, spec.shape, generator=gen, dtype=torch.int32, device=device)
     # Drawn in float32 then rounded, so the bfloat16 and float32 forms of a seed agree.
-    if spec.role == "norm":
+    if spec.role == "norm_offset":
+        t = norm_jitter * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+    elif spec.role == "norm":
         t = 1.0 + norm_jitter * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
     else:
         t = torch.empty(spec.shape, dtype=dtype, device=device)
@@ -47,7 +53,7 @@ def random_tensors(specs: Sequence[WeightSpec], seed: int, sigma: float = 0.02, 
                    ) -> Dict[str, torch.Tensor]:
     out = {}
     for index, spec in enumerate(sorted((s for s in specs if s.load), key=lambda s: s.name)):
-        dt = (norm_dtype or dtype) if spec.role == "norm" else dtype
+        dt = (norm_dtype or dtype) if spec.role in ("norm", "norm_offset") else dtype
         out[spec.name] = _make(spec, seed, index, sigma, norm_jitter, dt, device)
     return out
 
