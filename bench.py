@@ -53,6 +53,132 @@ WORKLOADS = {
 }
 
 
+# ``--workload rusadra``: the Rusadra design (latent attention and generalized-delta layers in turn, every layer with
+# a table-routed mixture of experts) beside the Qwen3 dense decoder at equal width, depth, vocabulary and active
+# feed-forward width, at two sizes that resemble real layers; prefill and decode throughput and, per kernel class,
+# the fraction of the device's peaks (``--steps`` decode steps are timed per point).
+DESIGN_SIZES = {
+    "w2048": dict(width=2048, vocab=65536, layers=8, heads=16, dim=128, rot=64, vdim=128, rank=512, window=1024,
+                  delta_heads=32, delta_dim=64, decay_rank=64, experts=32, top=4, ff=1024),
+    "w4096": dict(width=4096, vocab=65536, layers=4, heads=32, dim=128, rot=64, vdim=128, rank=512, window=2048,
+                  delta_heads=64, delta_dim=64, decay_rank=64, experts=64, top=8, ff=1536),
+}
+
+
+def design_configs(z):
+    """(Rusadra config.json, Qwen3 config.json) of one entry of DESIGN_SIZES."""
+    latent = {"type": "latent_attention", "mixer": {
+        "heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["rank"],
+        "scale": (z["dim"] + z["rot"]) ** -0.5, "mask": {"size": z["window"]}, "rot": {"base": 1e6, "dims": z["rot"]}}}
+    delta = {"type": "general_delta", "mixer": {"heads": z["delta_heads"], "dim": z["delta_dim"],
+                                                "decay_rank": z["decay_rank"]}}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]}}
+    rus = {"architecture": "Rusadra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+           "logit_softcap": 30.0,
+           "layers": [dict(delta if i % 2 == 0 else latent, mlp=mlp) for i in range(z["layers"])]}
+    qwen = dict(QWEN3_8B, num_hidden_layers=z["layers"], hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=max(1, z["heads"] // 4), head_dim=128, intermediate_size=z["top"] * z["ff"],
+                vocab_size=z["vocab"], eos_token_id=1)
+    return rus, qwen
+
+
+def run_design(args):
+    import numpy as np
+    import torch
+    import llm_rs_b200  # noqa: F401
+    from llm_rs_b200 import ops
+    from llm_rs_b200.config import resolve_architecture
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    from llm_rs_b200.parts import DecoderModel
+    from llm_rs_b200.profiling import Profiler
+    from llm_rs_b200.weights import random_tensors
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    K, W = max(4, args.steps), max(3, args.warmup)
+    page, ctx_len, n_prompt = 16, args.context, args.prefill_tokens
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    sampler.start()
+    out = {}
+    for size, z in DESIGN_SIZES.items():
+        for raw in design_configs(z):
+            entry = resolve_architecture(raw)
+            spec = entry.build_spec(entry.config_cls.from_dict(raw))
+            name = f"{entry.name} {size}"
+            tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=2, sigma=0.02, dtype=torch.bfloat16,
+                                     device="cuda:0")
+            runner = ModelRunner(spec, tensors, torch.bfloat16, "cuda:0", max_tokens=64 * (ctx_len + 64) + n_prompt + 64,
+                                 page_size=page, max_requests=65)
+            del tensors
+            for kv in runner.storage.kv:
+                for i in range(kv.size(0)):
+                    kv[i].normal_(0.0, 1.0)
+            V = spec.vocab_size
+            res = {"weights_gb": round(torch.cuda.memory_allocated() / 1e9, 2)}
+
+            def prefill_once():
+                runner.step([StepEntry("p", rng.integers(0, V, n_prompt).tolist(), [n_prompt - 1])])
+                runner.release("p")
+            times = []
+            for it in range(4):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                prefill_once()
+                b.record()
+                torch.cuda.synchronize()
+                if it:
+                    times.append(a.elapsed_time(b))
+            res["prefill"] = {"tokens": n_prompt, "ms": round(statistics.median(times), 3),
+                              "tokens_per_s": round(n_prompt / statistics.median(times) * 1e3, 1)}
+            with Profiler(pk["hbm_gbs"], pk["bf16_tflops"], nvtx=False) as prof:
+                prefill_once()
+            res["prefill_kernels"] = [{k: r[k] for k in ("class", "calls", "us_each", "share", "gb_s", "tflop_s", "bound", "frac")}
+                                      for r in prof.classes()[:14]]
+            print(f"[bench] {name}: prefill of {n_prompt} tokens {res['prefill']['ms']} ms\n" + prof.report(),
+                  file=sys.stderr, flush=True)
+            runner.use_graphs = not args.no_graphs
+            for batch in (8, 64):
+                ids = [f"d{batch}_{i}" for i in range(batch)]
+                for rid in ids:      # cached context without a prefill: the step reads the same bytes whatever they hold
+                    rec = runner.manager.admit(rid)
+                    runner.storage.reset_slot(rec.slot)
+                    runner.manager.reserve(rid, ctx_len - W - K)
+                    runner.manager.commit(rid, ctx_len - W - K)
+                toks = rng.integers(0, V, (W + K, batch)).tolist()
+                for s in range(W):
+                    runner.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                for s in range(W, W + K):
+                    runner.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
+                b.record()
+                torch.cuda.synchronize()
+                ms = a.elapsed_time(b) / K
+                res[f"decode_b{batch}"] = {"context": ctx_len, "ms_per_step": round(ms, 4),
+                                           "tokens_per_s": round(batch / ms * 1e3, 1)}
+                if batch == 8:
+                    runner.use_graphs = False
+                    with Profiler(pk["hbm_gbs"], pk["bf16_tflops"], nvtx=False) as prof:
+                        runner.step([StepEntry(r, [1], [0]) for r in ids])
+                    runner.use_graphs = not args.no_graphs
+                    res["decode_b8_kernels"] = [{k: r[k] for k in ("class", "calls", "us_each", "share", "gb_s", "tflop_s", "bound", "frac")}
+                                                for r in prof.classes()[:14]]
+                    print(f"[bench] {name}: decode step at batch 8, context {ctx_len}: {ms:.3f} ms\n" + prof.report(),
+                          file=sys.stderr, flush=True)
+                for rid in ids:
+                    runner.release(rid)
+            runner.check_kernels()
+            out[name] = res
+            del runner
+            torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    print(json.dumps({"workload": "rusadra", "dtype": "bf16", "data": "synthetic: random weights, random token ids",
+                      "peaks": pk, "sizes": DESIGN_SIZES, "results": out, "launches": ops.launch_count, "clocks": clocks}))
+    return 0
+
+
 NOMINAL = {"hbm_gbs": 7700.0, "bf16_tflops": 2250.0}     # HBM3e of the HGX B200, dense bfloat16
 REPEATS = 5
 
@@ -245,7 +371,7 @@ def main():
     ap.add_argument("--profile", action="store_true", help="instead of the benchmark: time every kernel class of one "
                     "decode step and of the prefill with CUDA events (eager launches, NVTX ranges) and print a table "
                     "with bytes, flops and the fraction of the peaks to standard error, the rows as JSON to standard output")
-    ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS],
+    ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS, "rusadra"],
                     help="decode: the benchmark contract (default). mixed14b / stress32b: a whole serving run "
                     "through the engine on the layer sizes of Qwen3-14B / Qwen3-32B")
     ap.add_argument("--pool-tokens", type=int, default=0, help="size of the cache pool of a --workload run in "
@@ -260,6 +386,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload == "rusadra":
+        return run_design(args)
     if args.workload != "decode":
         return run_workload(args)
     W = max(3, args.warmup)

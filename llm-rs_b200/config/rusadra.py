@@ -46,15 +46,16 @@ class LatentMixer:
     vdim: int
     kv_rank: int
     scale: float
-    window: int
+    window: int          # mask.size: a token sees itself and the window - 1 before it; 0 (no mask key): all before it
     rot_base: float
     rot_dims: int
     kv_from: Optional[int] = None
 
     def to_dict(self) -> Dict[str, Any]:
         d = {"heads": self.heads, "dim": self.dim, "rot_dim": self.rot_dim, "vdim": self.vdim,
-             "kv_rank": self.kv_rank, "scale": self.scale, "mask": {"size": self.window},
-             "rot": {"base": self.rot_base, "dims": self.rot_dims}}
+             "kv_rank": self.kv_rank, "scale": self.scale, "rot": {"base": self.rot_base, "dims": self.rot_dims}}
+        if self.window:
+            d["mask"] = {"size": self.window}
         if self.kv_from is not None:
             d["kv_from"] = self.kv_from
         return d
@@ -125,7 +126,7 @@ class RusadraConfig:
                     heads=_get(m, "heads", int, where, 1), dim=_get(m, "dim", int, where, 1),
                     rot_dim=_get(m, "rot_dim", int, where, 2), vdim=_get(m, "vdim", int, where, 1),
                     kv_rank=_get(m, "kv_rank", int, where, 1), scale=_get(m, "scale", float, where),
-                    window=_get(m, "mask.size", int, where, 1), rot_base=_get(m, "rot.base", float, where),
+                    window=_get(m, "mask.size", int, where, 1, optional=True) or 0, rot_base=_get(m, "rot.base", float, where),
                     rot_dims=_get(m, "rot.dims", int, where, 0), kv_from=kv_from)
                 if mixer.rot_dims % 2 or mixer.rot_dims > mixer.rot_dim:
                     raise ConfigError(f"{where}: rot.dims {mixer.rot_dims} must be even and at most rot_dim {mixer.rot_dim}")

@@ -32,7 +32,8 @@ def build_spec(cfg: RusadraConfig) -> ModelSpec:
     for i, layer in enumerate(cfg.layers):
         if isinstance(layer.mixer, LatentMixer):
             owner = i if layer.mixer.kv_from is None else layer.mixer.kv_from
-            kept[owner] = max(kept.get(owner, 0), layer.mixer.window)
+            w = layer.mixer.window
+            kept[owner] = w if owner not in kept else (0 if 0 in (w, kept[owner]) else max(w, kept[owner]))
     layers, order = [], []
     for i, layer in enumerate(cfg.layers):
         m = layer.mixer

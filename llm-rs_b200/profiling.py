@@ -74,7 +74,43 @@ def _cost_rows(*tensors_from):
     return cost
 
 
+def _cost_grouped(x, w, out, tiles, n_tiles, src, w2=None, **k):
+    rows, (G, N, K) = out.size(0), w.shape
+    both = 2 if w2 is not None else 1
+    # Every expert's weights are read at least once when at least that many rows are there; the rows read and written.
+    touched = min(G, max(rows, 1))
+    return (f"{G}x{N}x{K}{' gated' if w2 is not None else ''}",
+            touched * N * K * w.element_size() * both + rows * (K * x.element_size() + N * out.element_size()),
+            2.0 * rows * N * K * both)
+
+
+def _cost_batched(x, w, out, **k):
+    M, B, K = x.shape
+    N = w.size(1)
+    return f"{B}x{N}x{K}", _nbytes(w) + M * B * (K * x.element_size() + N * out.element_size()), 2.0 * M * B * N * K
+
+
+def _cost_latent_attention(qa, q, gate, cache, table, ctx, out, n_heads, dn, dr, rank, page_size, window, scale, **k):
+    pos = ctx.positions.double() + 1
+    pairs = (pos.clamp(max=window) if window > 0 else pos).sum()       # (query, key) pairs, counted on the device
+    c, n = ctx.cached_len.double(), ctx.n_new.double()
+    keys = ((c.clamp(max=window) if window > 0 else c) + n).sum()      # cached rows that must be read at least once
+    row = (rank + dr) * cache.element_size()
+    return (f"{qa.size(0)} tokens", lambda: int(float(keys) * row) + 2 * _nbytes(qa),
+            lambda: 2.0 * float(pairs) * n_heads * (2 * rank + dr))
+
+
+def _cost_delta_rule(r, k, v, gate, a_raw, decay_raw, decay_bias, a_bias, norm_w, state, ctx, n_heads, d, *a, **kw):
+    tokens = r.size(0)
+    return (f"{tokens} tokens", tokens * n_heads * d * (6 * r.element_size() + 4) + 2 * ctx.n_requests * n_heads * d * d * 4,
+            8.0 * tokens * n_heads * d * d)
+
+
 WRAPPED: Dict[str, Callable] = {
+    "gemm_grouped": _cost_grouped, "gemm_batched": _cost_batched, "latent_attention": _cost_latent_attention,
+    "delta_rule": _cost_delta_rule, "token_shift": _cost_rows(0), "outnorm_add": _cost_rows(0, 1),
+    "latent_prepare": _cost_rows(0), "tanh_slice": _cost_rows(0), "softcap_": _cost_rows(0),
+    "moe_route_table": _cost_rows(0), "moe_sort": _cost_rows(0), "moe_combine": _cost_rows(0),
     "gemm_bf16": _cost_gemm, "gemm_qkv_rope": _cost_qkv, "gemm_f32": _cost_gemm_f32, "library_gemm": _cost_library,
     "attn_decode": _cost_attn_decode, "attn_prefill": _cost_attn_prefill,
     "add_rmsnorm": _cost_rows(0), "embedding": lambda table, ids, *a, **k: ("", ids.numel() * table.size(1) * (table.element_size() + 4), 0.0),

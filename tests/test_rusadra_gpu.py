@@ -1,0 +1,415 @@
+"""The Rusadra design on the GPU against the plain implementation (tests/plain_rusadra.py, float64, no cache):
+each mechanism's kernel alone, then whole models replayed whole, with a tail decoded token by token, in portions
+down to two tokens and in mixed batches with so few pages and slots that they are used again; float32 and bfloat16;
+greedy generation through the engine's entry point and scheduler, with and without CUDA graphs; the trace program."""
+import json
+import math
+import os
+import subprocess
+import sys
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import plain_rusadra as P
+import replay_util as RU
+from rusadra_configs import RUSADRA, write_rusadra_model
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 2e-4          # float32 engine against float64: rounding only
+TOL_BF16_REL = 0.04     # of the largest logit; a wrong key, state or expert moves logits by their own size
+DEV = "cuda:0"
+LENGTHS = {"A": [2, 19, 40, 77, 131, 260], "B": [1, 9, 33, 70, 128, 161], "C": [5, 31, 66, 150, 300]}
+MODES = ["whole", "tail", "portions", "mixed"]
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    folder = tmp_path_factory.mktemp("rusadra")
+    out = {}
+    for name in RUSADRA:
+        path = write_rusadra_model(name, str(folder))
+        cfg, w = P.load_model_dir(path)
+        rng = np.random.default_rng(7 + ord(name))
+        reqs = {f"r{i}": rng.integers(0, cfg["vocab"], n).tolist() for i, n in enumerate(LENGTHS[name])}
+        ref = {r: P.forward(cfg, w, toks).numpy() for r, toks in reqs.items()}
+        out[name] = (path, cfg, w, reqs, ref)
+    return out
+
+
+def _ctx(n_new, cached, slots=None):
+    """The index arrays of a step, as the step function gives them to the kernels."""
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    q_start = np.concatenate([[0], np.cumsum(n_new)[:-1]]).tolist()
+    token_req = [r for r, n in enumerate(n_new) for _ in range(n)]
+    positions = [c + i for c, n in zip(cached, n_new) for i in range(n)]
+    return SimpleNamespace(n_tokens=sum(n_new), n_requests=len(n_new), q_start=i32(q_start), n_new=i32(n_new),
+                           cached_len=i32(cached), slot_ids=i32(slots if slots is not None else range(len(n_new))),
+                           token_req=i32(token_req), positions=i32(positions))
+
+
+def _assert_logits(got, ref, dtype, what):
+    """float32: every position within TOL_F32. bfloat16: a recurrent head whose output is nearly orthogonal to its
+    query is divided by a tiny root mean square, which magnifies rounding at that one position (the float32 engine
+    shows the same positions at 20 times its usual error), so 1 % of the positions may exceed the tolerance, none
+    by more than 2.5 times; a wrong key, state or expert moves every later position by the logits' own size."""
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    diffs = {k: float(np.abs(row.astype(np.float64) - ref[k[0]][k[1]]).max()) for k, row in got.items()}
+    assert all(np.isfinite(d) for d in diffs.values()), what
+    worst = max(diffs, key=diffs.get)
+    if dtype == "float32":
+        assert diffs[worst] <= TOL_F32, f"{what}: max |diff| {diffs[worst]:.3e} at {worst}"
+        return
+    tol = TOL_BF16_REL * scale
+    over = [k for k, d in diffs.items() if d > tol]
+    assert diffs[worst] <= 2.5 * tol and len(over) <= max(1, len(diffs) // 100), \
+        f"{what}: max |diff| {diffs[worst]:.3e} at {worst}, {len(over)} of {len(diffs)} over {tol:.3e}"
+
+
+# ---- mechanisms alone -----------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_token_shift_keeps_the_previous_row_per_request(dtype):
+    """Two requests fed in unequal portions over three steps (one sits a step out, one comes as single tokens);
+    slots that are not the requests' order."""
+    from llm_rs_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    D = 70
+    seqs = [torch.randn(9, D, generator=g), torch.randn(5, D, generator=g)]
+    mu = torch.rand(D, generator=g)
+    want = [P.token_shift(s.double(), mu.double()) for s in seqs]
+    state = torch.zeros(4, D, device=DEV)
+    state[1] = 99.0      # another request's slot must stay untouched
+    got = [[], []]
+    for cuts in ([(0, 0, 4), (1, 0, 1)], [(0, 4, 1)], [(1, 1, 4), (0, 5, 4)]):
+        x = torch.cat([seqs[r][a:a + n] for r, a, n in cuts]).to(DEV)
+        ctx = _ctx([n for _, _, n in cuts], [a for _, a, _ in cuts], [3 if r == 0 else 2 for r, _, _ in cuts])
+        y = ops.token_shift(x, mu.to(DEV), state, ctx, dtype).float().cpu()
+        at = 0
+        for r, a, n in cuts:
+            got[r].append(y[at:at + n])
+            at += n
+    for r in range(2):
+        d = (torch.cat(got[r]).double() - want[r]).abs().max().item()
+        assert d <= (1e-6 if dtype == torch.float32 else 0.03), d
+    assert torch.all(state[1] == 99.0) and torch.allclose(state[3].cpu(), seqs[0][-1])
+    plain = ops.token_shift(seqs[0].to(DEV), None, None, None, dtype).float().cpu()
+    assert (plain - seqs[0]).abs().max().item() <= (0 if dtype == torch.float32 else 0.03)
+
+
+def test_norm_on_a_branch_output_and_soft_cap():
+    from llm_rs_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    h, y, w = torch.randn(6, 90, generator=g), 3 * torch.randn(6, 90, generator=g), 0.3 * torch.randn(90, generator=g)
+    want = h.double() + P.offset_norm(y.double(), w.double(), 1e-3)
+    got = ops.outnorm_add(h.to(DEV).clone(), y.to(DEV), (1.0 + w).to(DEV), 1e-3).cpu()
+    assert (got.double() - want).abs().max().item() < 1e-5
+    got16 = ops.outnorm_add(h.to(DEV).clone(), y.to(DEV).bfloat16(), (1.0 + w).to(DEV), 1e-3).cpu()
+    want16 = h.double() + P.offset_norm(y.bfloat16().double(), w.double(), 1e-3)
+    assert (got16.double() - want16).abs().max().item() < 1e-5
+    z = 40 * torch.randn(5, 33, generator=g)
+    got = ops.softcap_(z.to(DEV).clone(), 7.5).cpu()
+    assert (got.double() - 7.5 * torch.tanh(z.double() / 7.5)).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts,top,n_tokens", [(4, 2, 50), (3, 3, 7), (1, 1, 5), (37, 4, 300), (8, 1, 1)])
+def test_mixture_of_experts_against_plain(dtype, experts, top, n_tokens):
+    """Routing by the table, the sort by expert, both grouped products and the weighted sum; token ids repeat, some
+    experts get no token, tiles of rows are cut inside an expert's run (300 tokens x 4 over 37 experts)."""
+    from llm_rs_b200 import ops
+    from llm_rs_b200.parts import Runtime
+    from llm_rs_b200.parts.moe import MixtureOfExperts
+    g = torch.Generator().manual_seed(experts * 100 + top)
+    D, F, V = 48, 40, 23
+    part = MixtureOfExperts(D, F, experts, top, vocab_size=V, limit=0.8, alpha=1.702, up_shift=1.0, prefix="f.")
+    w = {}
+    for s in part.weight_specs():
+        if s.role == "expert_table":
+            w[s.name] = torch.rand(V, experts, generator=g).argsort(1)[:, :top].int()
+        else:
+            w[s.name] = (0.3 * torch.randn(s.shape, generator=g)).bfloat16().float()
+    part.bind({k: (v.to(DEV) if v.dtype == torch.int32 else v.to(DEV, dtype)) for k, v in w.items()},
+              Runtime(torch.device(DEV), dtype, 64))
+    tokens = torch.randint(0, V, (n_tokens,), generator=g)
+    x = torch.randn(n_tokens, D, generator=g)
+    xin = x.bfloat16().float() if dtype == torch.bfloat16 else x
+    want = P.table_moe(xin.double(), tokens, {k: (v.double() if v.is_floating_point() else v.long()) for k, v in w.items()},
+                       "f.", {"router": {"top": top}, "expert": {"limit": 0.8}})
+    ctx = SimpleNamespace(token_ids=tokens.int().to(DEV))
+    got = part.forward(x.to(DEV), ctx).cpu()
+    tol = 1e-5 if dtype == torch.float32 else 0.02 * want.abs().max().item()
+    assert (got.double() - want).abs().max().item() <= tol
+    # The sort: a permutation, rows of one expert together, tiles that cover exactly the rows.
+    expert_of, _ = ops.moe_route_table(ctx.token_ids, part.table, experts)
+    row_of, src, tiles, n_tiles = ops.moe_sort(expert_of, top, experts)
+    row_of, src, tiles, e = row_of.cpu(), src.cpu(), tiles.cpu()[: int(n_tiles.item())], expert_of.cpu()
+    assert sorted(row_of.tolist()) == list(range(n_tokens * top))
+    by_row = torch.empty_like(e)
+    by_row[row_of.long()] = e
+    assert torch.all(by_row[1:] >= by_row[:-1])
+    assert torch.equal(src[row_of.long()], torch.arange(n_tokens * top, dtype=torch.int32) // top)
+    covered = []
+    for ex, first, n in tiles.tolist():
+        assert 0 < n <= ops.GROUPED_TILE_ROWS and torch.all(by_row[first:first + n] == ex)
+        covered += list(range(first, first + n))
+    assert covered == list(range(n_tokens * top))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,d,rank", [(2, 16, 4), (1, 48, 7), (3, 64, 16), (1, 128, 8), (2, 100, 8)])
+def test_delta_rule_mixer_against_plain(dtype, heads, d, rank):
+    """The mixer part alone: three requests in one step (a long portion, a short one, a single token), then each
+    continued from its state; slots in another order than the requests."""
+    from llm_rs_b200.parts import Runtime
+    from llm_rs_b200.parts.delta_rule import GeneralDelta
+    g = torch.Generator().manual_seed(heads * 1000 + d)
+    D = 40
+    part = GeneralDelta(D, heads, d, rank, norm_eps=1e-5, prefix="m.")
+    w = {s.name: ((0.5 if len(s.shape) > 1 else 1.0) * torch.randn(s.shape, generator=g) / math.sqrt(s.shape[-1] if len(s.shape) > 1 else 1)
+                  ).bfloat16().float() for s in part.weight_specs()}
+    part.bind({k: v.to(DEV, torch.float32 if v.dim() == 1 else dtype) for k, v in w.items()},
+              Runtime(torch.device(DEV), dtype, 64))
+    lens = [37, 6, 1]
+    more = [1, 9, 20]
+    seqs = [torch.randn(a + b, D, generator=g) for a, b in zip(lens, more)]
+    if dtype == torch.bfloat16:
+        seqs = [s.bfloat16().float() for s in seqs]
+    want = [P.general_delta(s.double(), {k: v.double() for k, v in w.items()}, "m.", {"heads": heads, "dim": d}, 1e-5)[0]
+            for s in seqs]
+    state = torch.zeros(5, heads, d, d, device=DEV)
+    slots = [4, 0, 2]
+    cache = SimpleNamespace(state={GeneralDelta.STATE: state})
+    got = [[], [], []]
+    for first in (True, False):
+        parts = [s[:a] if first else s[a:] for s, a in zip(seqs, lens)]
+        ctx = _ctx([p.shape[0] for p in parts], [0, 0, 0] if first else lens, slots)
+        y = part.forward(torch.cat(parts).to(DEV, dtype), ctx, cache).float().cpu()
+        at = 0
+        for r, p in enumerate(parts):
+            got[r].append(y[at:at + p.shape[0]])
+            at += p.shape[0]
+    for r in range(3):
+        scale = want[r].abs().max().item()
+        d_ = (torch.cat(got[r]).double() - want[r]).abs().max().item()
+        assert d_ <= (2e-5 * max(1, scale) if dtype == torch.float32 else 0.03 * scale), (r, d_, scale)
+    assert torch.all(state[1] == 0) and torch.all(state[3] == 0)
+
+
+def _latent_setup(dtype, heads, dn, dr, dv, rank, window, rot_dims, page_size, n_pages, seed):
+    from llm_rs_b200.parts import Runtime
+    from llm_rs_b200.parts.latent_attention import LatentAttention
+    g = torch.Generator().manual_seed(seed)
+    D = 56
+    part = LatentAttention(D, heads, dn, dr, dv, rank, scale=0.31, rot_base=3000.0, rot_dims=rot_dims, window=window,
+                           norm_eps=1e-5, prefix="m.")
+    w = {s.name: (torch.randn(s.shape, generator=g) * (1.0 if len(s.shape) == 1 else 1.5 / math.sqrt(s.shape[-1]))
+                  ).bfloat16().float() for s in part.weight_specs()}
+    part.bind({k: v.to(DEV, torch.float32 if v.dim() == 1 else dtype) for k, v in w.items()},
+              Runtime(torch.device(DEV), dtype, 4096))
+    pages = torch.zeros(n_pages, 1, page_size * (rank + dr), dtype=dtype, device=DEV)
+    planes = [pages[:, :, : page_size * rank].unflatten(2, (page_size, rank)),
+              pages[:, :, page_size * rank:].unflatten(2, (page_size, dr))]
+    m = {"heads": heads, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": rank, "scale": 0.31,
+         "mask": {"size": window if window else 1 << 30}, "rot": {"base": 3000.0, "dims": rot_dims}}
+    return part, w, planes, m, g, D
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,dn,dr,dv,rank,window,rot_dims,page", [
+    (4, 16, 8, 24, 40, 20, 8, 16), (1, 24, 16, 40, 50, 0, 8, 8), (5, 8, 32, 8, 100, 7, 32, 4),
+    (8, 32, 32, 32, 128, 130, 32, 16), (3, 64, 64, 16, 300, 64, 64, 64)])
+def test_latent_attention_mixer_against_plain(dtype, heads, dn, dr, dv, rank, window, rot_dims, page):
+    """The mixer part alone over scattered pages: a prompt portion, then the rest in portions and single tokens,
+    beside a second request in the same steps; windows shorter and longer than a page, none at all."""
+    part, w, planes, m, g, D = _latent_setup(dtype, heads, dn, dr, dv, rank, window, rot_dims, page, 128, rank + heads)
+    lens = [150, 41]
+    seqs = [torch.randn(n, D, generator=g) for n in lens]
+    if dtype == torch.bfloat16:
+        seqs = [s.bfloat16().float() for s in seqs]
+    wd = {k: v.double() for k, v in w.items()}
+    want = [P.latent_attention(s.double(), wd, "m.", m, 1e-5)[0] for s in seqs]
+    perm = torch.randperm(128, generator=g).tolist()
+    width = -(-max(lens) // page)
+    table = torch.tensor([perm[:width], perm[width:2 * width]], dtype=torch.int32, device=DEV)
+    cache = SimpleNamespace(planes=planes, block_table=table, page_size=page, owns=True, state={})
+    at, got = [0, 0], [[], []]
+    cuts = [(97, 30), (2, 1), (1, 1), (30, 2), (1, 1), (19, 6)]
+    for cut in cuts:
+        ctx = _ctx(list(cut), list(at))
+        x = torch.cat([s[a:a + n] for s, a, n in zip(seqs, at, cut)]).to(DEV, dtype)
+        y = part.forward(x, ctx, cache).float().cpu()
+        o = 0
+        for r, n in enumerate(cut):
+            got[r].append(y[o:o + n])
+            o += n
+            at[r] += n
+    for r in range(2):
+        scale = want[r].abs().max().item()
+        d = (torch.cat(got[r]).double() - want[r]).abs().max().item()
+        assert d <= (3e-5 * max(1, scale) if dtype == torch.float32 else 0.03 * scale), (r, d, scale)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("decode", [False, True])
+def test_latent_attention_window_edge(dtype, decode):
+    """A key at a page's first row is replaced by a row 25 times larger (its rotated key part then dominates or
+    vanishes from the softmax of a window of 13). The output must move when that key is the last one inside the
+    window and must stay bit for bit when it is one step outside. Checked for a query inside a prompt's portion and
+    for one decoded alone."""
+    window, page = 13, 8
+    part, w, planes, m, g, D = _latent_setup(dtype, 2, 16, 8, 12, 24, window, 8, page, 32, 5)
+    n = 96
+    base = torch.randn(n, D, generator=g)
+    other = 25.0 * torch.randn(D, generator=g)
+    key_at = 48                                    # first row of a page
+    outs = {}
+    for name, query_at in (("inside", key_at + window - 1), ("outside", key_at + window)):
+        for planted in (False, True):
+            x = base.clone()
+            if planted:
+                x[key_at] = other
+            x = x.bfloat16().float() if dtype == torch.bfloat16 else x
+            want = P.latent_attention(x.double(), {k: v.double() for k, v in w.items()}, "m.", m, 1e-5)[0][query_at]
+            for p in planes:
+                p.zero_()
+            table = torch.arange(31, -1, -1, dtype=torch.int32, device=DEV)[None, : n // page].contiguous()
+            cache = SimpleNamespace(planes=planes, block_table=table, page_size=page, owns=True, state={})
+            if decode:
+                part.forward(x[:query_at].to(DEV, dtype), _ctx([query_at], [0]), cache)
+                y = part.forward(x[query_at:query_at + 1].to(DEV, dtype), _ctx([1], [query_at]), cache)[0]
+            else:
+                y = part.forward(x[: query_at + 3].to(DEV, dtype), _ctx([query_at + 3], [0]), cache)[query_at]
+            scale = want.abs().max().item()
+            d = (y.float().cpu().double() - want).abs().max().item()
+            assert d <= (3e-5 * max(1, scale) if dtype == torch.float32 else 0.03 * scale), (name, planted, d, scale)
+            outs[(name, planted)] = y.float().cpu()
+    moved = (outs[("inside", True)] - outs[("inside", False)]).abs().max().item()
+    still = (outs[("outside", True)] - outs[("outside", False)]).abs().max().item()
+    assert moved > 0.02 * outs[("inside", False)].abs().max().item(), moved
+    assert still == 0.0, still
+
+
+# ---- whole models -----------------------------------------------------------------------------------
+def _steps(mode, reqs):
+    if mode == "tail":
+        return RU.tail_one_by_one(reqs, tail=70)      # longer than every window but C's widest
+    if mode == "portions":
+        return RU.portions(reqs, sizes=(1, 1, 2, 7, 2, 13, 5, 2, 31, 3, 17, 2, 64))
+    return {"whole": RU.whole, "mixed": RU.mixed}[mode](reqs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", list(RUSADRA))
+def test_replay_matches_plain(models, name, mode, dtype):
+    from llm_rs_b200.engine import ModelRunner
+    path, cfg, w, reqs, ref = models[name]
+    steps = _steps(mode, reqs)
+    runner = ModelRunner.from_model_dir(path, dtype=getattr(torch, dtype), max_tokens=RU.live_token_peak(steps),
+                                        page_size=RUSADRA[name][3], max_requests=4)
+    free_before = [runner.manager.free_pages(g) for g in range(len(runner.manager.groups))]
+    got = RU.run_steps(runner, steps)
+    assert [runner.manager.free_pages(g) for g in range(len(runner.manager.groups))] == free_before, "pages were lost"
+    runner.check_kernels()
+    assert len(got) == sum(len(t) for t in reqs.values())
+    _assert_logits(got, ref, dtype, f"{name} {mode} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [21, 22])
+@pytest.mark.parametrize("name", list(RUSADRA))
+def test_mixed_replay_with_other_cuts_and_slots_used_again(models, name, seed, dtype):
+    """Mixed batches with other seeds and portion sizes, two or three live requests, the requests twice over, so that
+    every state slot and page serves several requests."""
+    from llm_rs_b200.engine import ModelRunner
+    path, cfg, w, reqs, ref = models[name]
+    rng = np.random.default_rng(seed)
+    sizes = tuple(int(x) for x in rng.choice([2, 3, 7, 16, 31, 33, 64, 65, 129], size=5, replace=False))
+    twice = {**reqs, **{r + "again": t for r, t in reqs.items()}}
+    ref2 = {**ref, **{r + "again": v for r, v in ref.items()}}
+    steps = RU.mixed(twice, seed=seed, max_live=2 + seed % 2, decode_tail=5 + seed % 7, sizes=sizes)
+    runner = ModelRunner.from_model_dir(path, dtype=getattr(torch, dtype), max_tokens=RU.live_token_peak(steps),
+                                        page_size=RUSADRA[name][3], max_requests=3)
+    got = RU.run_steps(runner, steps)
+    assert len(got) == 2 * sum(len(t) for t in reqs.values())
+    _assert_logits(got, ref2, dtype, f"{name} seed {seed} {dtype}")
+
+
+def test_a_far_window_and_an_all_state_model_run_beyond_the_pool(models, tmp_path):
+    """A request of 400 tokens through model A with pages for 128: its attention windows give pages back as they
+    pass, the recurrent layers hold none. The last tokens are decoded one by one."""
+    from llm_rs_b200.engine import ModelRunner
+    path, cfg, w, reqs, ref = models["A"]
+    toks = np.random.default_rng(5).integers(0, cfg["vocab"], 400).tolist()
+    want = P.forward(cfg, w, toks).numpy()
+    runner = ModelRunner.from_model_dir(path, dtype=torch.float32, max_tokens=128, page_size=16, max_requests=2)
+    steps = RU.tail_one_by_one({"long": toks}, tail=90)
+    steps = [{"entries": [{"id": "long", "tokens": toks[a:a + 50], "want": list(range(len(toks[a:a + 50])))}], "end": []}
+             for a in range(0, 300, 50)] + steps[1:]
+    steps[5]["entries"][0]["tokens"] = toks[250:310]
+    steps[5]["entries"][0]["want"] = list(range(60))
+    got = RU.run_steps(runner, steps)
+    worst, where, n = RU.max_diff(got, {"long": want})
+    assert n == 400 and worst <= TOL_F32, (worst, where)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(RUSADRA))
+def test_greedy_generation_through_the_engine(models, name, dtype, graphs):
+    """Prompts of unequal length through ``Engine.generate``: scheduler, prompt portions, decoding (captured in CUDA
+    graphs or not), the device sampler's argmax. float32 gives the plain implementation's tokens; bfloat16 may choose
+    another token only where the plain logits of the two are closer than its rounding."""
+    from llm_rs_b200.engine import Engine, EngineConfig
+    from llm_rs_b200.sampling import SamplingParams
+    path, cfg, w, reqs, ref = models[name]
+    prompts = [reqs[r][:n] for r, n in zip(list(reqs)[1:4], (9, 33, 20))]
+    engine = Engine(EngineConfig(model_path=path, block_pool_size=64, page_size=RUSADRA[name][3], dtype=dtype,
+                                 max_requests=4, cuda_graphs=graphs, prefill_chunk=16, max_tokens_per_step=24))
+    got = engine.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True))
+    for prompt, new in zip(prompts, got):
+        assert len(new) == 12
+        if dtype == "float32":
+            assert new == P.greedy_generate(cfg, w, prompt, 12)
+        else:
+            toks = list(prompt)
+            for t in new:
+                row = P.forward(cfg, w, toks)[-1]
+                assert float(row.max() - row[t]) <= 0.05 * float(row.abs().max()), "bfloat16 strays from the plain logits"
+                toks.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_program_on_a_rusadra_folder(models, tmp_path, dtype):
+    """bin/trace_run picks the design by config.json and replays a mixed trace with four state slots."""
+    path, cfg, w, reqs, ref = models["B"]
+    steps = RU.want_only(RU.mixed(reqs, seed=9), {r: set(range(0, len(t), 3)) | {len(t) - 1} for r, t in reqs.items()})
+    out_dir = tmp_path / "out"
+    lines = [json.dumps({"step": i, **st}) for i, st in enumerate(steps)]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", dtype, "--out", str(out_dir),
+         "--max-tokens", str(RU.live_token_peak(steps)), "--max-requests", "4"],
+        input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[:len(steps)] == [f"done {i}" for i in range(len(steps))]
+    at, worst, V = {}, 0.0, cfg["vocab"]
+    for i, st in enumerate(steps):
+        n_want = sum(len(e["want"]) for e in st["entries"])
+        if not n_want:
+            assert not (out_dir / f"{i}.f32").exists()
+        else:
+            data = np.fromfile(out_dir / f"{i}.f32", dtype="<f4").reshape(-1, V)
+            assert data.shape[0] == n_want
+        k = 0
+        for e in st["entries"]:
+            base = at.get(e["id"], 0)
+            for wnt in e["want"]:
+                worst = max(worst, float(np.abs(data[k] - ref[e["id"]][base + wnt]).max()))
+                k += 1
+            at[e["id"]] = base + len(e["tokens"])
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    assert worst <= (TOL_F32 if dtype == "float32" else TOL_BF16_REL * scale), worst
