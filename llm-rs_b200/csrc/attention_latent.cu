@@ -106,7 +106,8 @@ latent_attention_kernel(const TA* __restrict__ qa, long long qa_token, long long
                         const TA* __restrict__ gate, long long gate_stride, const TA* __restrict__ cache,
                         const int* __restrict__ table, int table_width, const int* __restrict__ positions,
                         const int* __restrict__ token_req, TA* __restrict__ out, long long out_token,
-                        long long out_head, int n_heads, int rank, int dr, int page_size, int window, float scale) {
+                        long long out_head, int n_heads, int rank, int dr, int page_size, int window, float scale,
+                        int split_keys, float* __restrict__ partial) {
   extern __shared__ float sm[];
   float* s_qr = sm;                                        // [HG][dr]
   float* s_m = s_qr + HG * dr;                             // [warps][HG]
@@ -116,7 +117,12 @@ latent_attention_kernel(const TA* __restrict__ qa, long long qa_token, long long
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pos = positions[t];
   const int* tab = table + (size_t)token_req[t] * table_width;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  int hi = pos;
+  if (partial != nullptr) {       // this block's share of the keys; it may be empty
+    lo += blockIdx.z * split_keys;
+    hi = min(pos, lo + split_keys - 1);
+  }
 
   float qv[HG][MAXC], acc[HG][MAXC], m[HG], l[HG];
 #pragma unroll
@@ -135,7 +141,7 @@ latent_attention_kernel(const TA* __restrict__ qa, long long qa_token, long long
   }
   __syncthreads();
   const size_t page_elems = (size_t)page_size * (rank + dr);
-  for (int j = lo + warp; j <= pos; j += LA_WARPS) {
+  for (int j = lo + warp; j <= hi; j += LA_WARPS) {
     int page = tab[j / page_size];
     page = LLMRS_CHECKED_PAGE(page, 3, j);
     const int slot = j % page_size;
@@ -196,8 +202,37 @@ latent_attention_kernel(const TA* __restrict__ qa, long long qa_token, long long
       num = fmaf(f, s_acc[(size_t)(w * HG + g) * rank + c], num);
       den = fmaf(f, s_l[w * HG + g], den);
     }
+    if (partial != nullptr) {     // [token, head, split, rank + 2]: unnormalised sum, then its maximum and its weight
+      float* p = partial + (((size_t)t * n_heads + h0 + g) * gridDim.z + blockIdx.z) * (rank + 2);
+      p[c] = num;
+      if (c == 0) p[rank] = mm, p[rank + 1] = den;
+      continue;
+    }
     const float gt = 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + h0 + g])));
     out[(size_t)t * out_token + (size_t)(h0 + g) * out_head + c] = from_float<TA>(num / den * gt);
+  }
+}
+
+// Merges the splits of a (token, head): out = sum_s e^(m_s - m) acc_s / sum_s e^(m_s - m) l_s, times sigmoid(gate).
+template <typename TA>
+__global__ void latent_combine_kernel(const float* __restrict__ partial, const TA* __restrict__ gate,
+                                      long long gate_stride, TA* __restrict__ out, long long out_token,
+                                      long long out_head, int n_heads, int rank, int n_splits) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* p = partial + ((size_t)t * n_heads + h) * n_splits * (rank + 2);
+  float mm = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, p[(size_t)s * (rank + 2) + rank]);
+  const float gt = 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + h])));
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float* ps = p + (size_t)s * (rank + 2);
+      if (ps[rank] == -INFINITY) continue;          // a split without keys
+      const float f = expf(ps[rank] - mm);
+      num = fmaf(f, ps[c], num);
+      den = fmaf(f, ps[rank + 1], den);
+    }
+    out[(size_t)t * out_token + (size_t)h * out_head + c] = from_float<TA>(num / den * gt);
   }
 }
 
@@ -206,29 +241,37 @@ static int launch_latent(int maxc, dim3 grid, size_t smem, cudaStream_t stream, 
                          long long qa_head, const void* q, long long q_stride, int q_rot_at, int q_head_width,
                          const void* gate, long long gate_stride, const void* cache, const int* table,
                          int table_width, const int* positions, const int* token_req, void* out, long long out_token,
-                         long long out_head, int n_heads, int rank, int dr, int page_size, int window, float scale) {
+                         long long out_head, int n_heads, int rank, int dr, int page_size, int window, float scale,
+                         int split_keys, float* partial) {
 #define LLMRS_LA(C)                                                                                                \
   latent_attention_kernel<TA, HG, C><<<grid, LA_WARPS * 32, smem, stream>>>(                                       \
       (const TA*)qa, qa_token, qa_head, (const TA*)q, q_stride, q_rot_at, q_head_width, (const TA*)gate,           \
       gate_stride, (const TA*)cache, table, table_width, positions, token_req, (TA*)out, out_token, out_head,      \
-      n_heads, rank, dr, page_size, window, scale)
+      n_heads, rank, dr, page_size, window, scale, split_keys, partial)
   if (maxc <= 2) LLMRS_LA(2);
   else if (maxc <= 4) LLMRS_LA(4);
   else if (maxc <= 8) LLMRS_LA(8);
   else LLMRS_LA(16);
 #undef LLMRS_LA
-  return llmrs_launch_status("latent_attention");
+  const int rc = llmrs_launch_status("latent_attention");
+  if (rc != 0 || partial == nullptr) return rc;
+  latent_combine_kernel<TA><<<dim3(grid.x, n_heads), 128, 0, stream>>>(partial, (const TA*)gate, gate_stride, (TA*)out,
+                                                                      out_token, out_head, n_heads, rank, grid.z);
+  return llmrs_launch_status("latent_attention (merge)");
 }
 
 // qa: folded queries [tokens, heads, rank] with strides; q: the projected queries, head h's rotated part at
 // q + t * q_stride + h * q_head_width + q_rot_at; gate: raw gate values [tokens, heads] (row stride given);
-// out: [tokens, heads, rank] with strides.
+// out: [tokens, heads, rank] with strides. n_splits > 1: every (token, head group) is cut into n_splits blocks of
+// split_keys keys from the first visible key on (n_splits * split_keys must cover the longest visible span), which
+// leave their partial softmaxes in `partial` (float32 [tokens, heads, n_splits, rank + 2]) for a second kernel to merge.
 LLMRS_API int llmrs_latent_attention(const void* qa, long long qa_token, long long qa_head, const void* q,
                                      long long q_stride, int q_rot_at, int q_head_width, const void* gate,
                                      long long gate_stride, const void* cache, int dtype, const int* table,
                                      int table_width, const int* positions, const int* token_req, void* out,
                                      long long out_token, long long out_head, int n_tokens, int n_heads, int rank,
-                                     int dr, int page_size, int window, float scale, cudaStream_t stream) {
+                                     int dr, int page_size, int window, float scale, int n_splits, int split_keys,
+                                     float* partial, cudaStream_t stream) {
   LLMRS_REQUIRE(n_tokens >= 0 && n_heads > 0 && rank > 0 && dr > 0 && page_size > 0, "latent_attention: bad sizes");
   LLMRS_REQUIRE(rank <= 512, "latent_attention: a latent of at most 512, got %d", rank);
   LLMRS_REQUIRE(window >= 0, "latent_attention: bad window");
@@ -237,11 +280,15 @@ LLMRS_API int llmrs_latent_attention(const void* qa, long long qa_token, long lo
   const int maxc = (rank + 31) / 32;
   const size_t smem = ((size_t)hg * dr + 2 * LA_WARPS * hg + (size_t)LA_WARPS * hg * rank) * sizeof(float);
   LLMRS_REQUIRE(smem <= 48 * 1024, "latent_attention: sizes need %zu bytes of shared memory", smem);
-  dim3 grid(n_tokens, (n_heads + hg - 1) / hg);
+  LLMRS_REQUIRE(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || (split_keys > 0 && partial != nullptr)),
+                "latent_attention: bad split");
+  if (n_splits == 1) partial = nullptr;
+  dim3 grid(n_tokens, (n_heads + hg - 1) / hg, n_splits);
   LLMRS_REQUIRE(grid.y <= 65535, "latent_attention: too many heads");
 #define LLMRS_LA_ARGS                                                                                              \
   maxc, grid, smem, stream, qa, qa_token, qa_head, q, q_stride, q_rot_at, q_head_width, gate, gate_stride, cache,  \
-      table, table_width, positions, token_req, out, out_token, out_head, n_heads, rank, dr, page_size, window, scale
+      table, table_width, positions, token_req, out, out_token, out_head, n_heads, rank, dr, page_size, window, scale, \
+      split_keys, partial
   if (dtype == LLMRS_F32) return hg == 4 ? launch_latent<float, 4>(LLMRS_LA_ARGS) : launch_latent<float, 1>(LLMRS_LA_ARGS);
   if (dtype == LLMRS_BF16)
     return hg == 4 ? launch_latent<__nv_bfloat16, 4>(LLMRS_LA_ARGS) : launch_latent<__nv_bfloat16, 1>(LLMRS_LA_ARGS);

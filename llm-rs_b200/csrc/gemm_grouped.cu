@@ -13,6 +13,7 @@
 // tile. bfloat16 operands are widened exactly; with `round_x` float32 rows of X are first rounded to bfloat16 (they
 // stand in for activations of that type).
 #include "common.cuh"
+#include "mma_util.cuh"
 
 constexpr int GG_BM = 64, GG_BN = 64, GG_BK = 16, GG_THREADS = 256;
 
@@ -133,6 +134,153 @@ __global__ void __launch_bounds__(GG_THREADS) gemm_grouped_kernel(const GroupedG
   }
 }
 
+// ---------------------------------------------------------------------------------
+// The same products on the tensor cores for bfloat16 operands (mma.sync m16n8k16, float32 accumulators): tiles of
+// 64 rows x 128 columns (64 of each product for the gated unit), k in steps of 32 through a double buffer of 16-byte asynchronous copies. Eight warps as
+// 2 x 4, each 32 rows x 32 (or 2 x 16) columns. Shared rows are 40 elements apart, which
+// spreads the fragments' 32-bit reads over all banks. A row's sums run over k in the same order whichever rows
+// share its tile. Needs K % 8 == 0 and 16-byte aligned rows of X and W.
+// ---------------------------------------------------------------------------------
+constexpr int GM_BM = 64, GM_BK = 32, GM_LD = GM_BK + 8, GM_THREADS = 256;
+// Columns of a tile: 128, or 64 of each of the two products of the gated unit (the same shared memory either way).
+template <bool GLU> struct GmCols { static constexpr int value = GLU ? 64 : 128; };
+
+template <typename TO, bool GLU>
+__global__ void __launch_bounds__(GM_THREADS) gemm_grouped_mma_kernel(const GroupedGemmArgs a) {
+  constexpr int GM_BN = GmCols<GLU>::value, NT = GM_BN / 32;      // NT: 8-column pieces per warp
+  __shared__ __align__(16) __nv_bfloat16 As[2][GM_BM][GM_LD];
+  __shared__ __align__(16) __nv_bfloat16 Bs[2][GM_BN][GM_LD];
+  __shared__ __align__(16) __nv_bfloat16 B2s[GLU ? 2 : 1][GLU ? GM_BN : 1][GM_LD];
+  __shared__ long long row_off[GM_BM];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int group, m0, rows;
+  if (a.tiles != nullptr) {
+    if ((int)blockIdx.y >= *a.n_tiles) return;
+    group = a.tiles[3 * blockIdx.y], m0 = a.tiles[3 * blockIdx.y + 1], rows = a.tiles[3 * blockIdx.y + 2];
+  } else {
+    group = blockIdx.z, m0 = blockIdx.y * GM_BM, rows = min(GM_BM, a.M - m0);
+  }
+  if (tid < GM_BM) {
+    long long off = -1;
+    if (tid < rows) {
+      const int row = m0 + tid;
+      off = (long long)(a.src ? a.src[row] : row) * a.x_stride + (a.tiles ? 0 : (long long)group * a.x_batch);
+    }
+    row_off[tid] = off;
+  }
+  __syncthreads();
+  const __nv_bfloat16* x = (const __nv_bfloat16*)a.x;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)a.w + (size_t)group * a.w_batch;
+  const __nv_bfloat16* w2 = GLU ? (const __nv_bfloat16*)a.w2 + (size_t)group * a.w_batch : nullptr;
+  const int n0 = blockIdx.x * GM_BN;
+
+  // Copies of one k step: A 64 rows x 4 pieces of 8 elements (one per thread), B 128 x 4 (two per thread).
+  const int a_row = tid >> 2, piece = (tid & 3) * 8;
+  const long long a_off = row_off[a_row];
+  auto issue = [&](int stage, int k0) {
+    const int k = k0 + piece;
+    const int kb = k < a.K ? min(16, (a.K - k) * 2) : 0;      // bytes of this piece inside K (K % 8 == 0: 0 or 16)
+    cp_async_16(&As[stage][a_row][piece], x + (a_off >= 0 ? a_off : 0) + (kb ? k : 0), a_off >= 0 ? kb : 0);
+#pragma unroll
+    for (int h = 0; h < GM_BN / 64; ++h) {
+      const int r = a_row + 64 * h, n = n0 + r;
+      const bool in = n < a.N;
+      cp_async_16(&Bs[stage][r][piece], w + (in ? (size_t)n * a.K : 0) + (kb ? k : 0), in ? kb : 0);
+      if (GLU) cp_async_16(&B2s[stage][r][piece], w2 + (in ? (size_t)n * a.K : 0) + (kb ? k : 0), in ? kb : 0);
+    }
+    cp_async_commit();
+  };
+
+  const int wm = (warp >> 2) * 32, wn = (warp & 3) * (8 * NT);
+  const int g = lane >> 2, t = lane & 3;
+  float acc[2][NT][4], acc2[GLU ? 2 : 1][GLU ? NT : 1][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[i][j][e] = 0.f;
+        if (GLU) acc2[i][j][e] = 0.f;
+      }
+  const int k_steps = (a.K + GM_BK - 1) / GM_BK;
+  issue(0, 0);
+  for (int ks = 0; ks < k_steps; ++ks) {
+    const int stage = ks & 1;
+    if (ks + 1 < k_steps) {
+      issue(stage ^ 1, (ks + 1) * GM_BK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GM_BK; kk += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = wm + 16 * i + g;
+        af[i][0] = *reinterpret_cast<const uint32_t*>(&As[stage][r][kk + 2 * t]);
+        af[i][1] = *reinterpret_cast<const uint32_t*>(&As[stage][r + 8][kk + 2 * t]);
+        af[i][2] = *reinterpret_cast<const uint32_t*>(&As[stage][r][kk + 2 * t + 8]);
+        af[i][3] = *reinterpret_cast<const uint32_t*>(&As[stage][r + 8][kk + 2 * t + 8]);
+      }
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int n = wn + 8 * j + g;
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Bs[stage][n][kk + 2 * t]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Bs[stage][n][kk + 2 * t + 8]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) mma_bf16_16816(acc[i][j], af[i], b0, b1);
+        if (GLU) {
+          const uint32_t c0 = *reinterpret_cast<const uint32_t*>(&B2s[stage][n][kk + 2 * t]);
+          const uint32_t c1 = *reinterpret_cast<const uint32_t*>(&B2s[stage][n][kk + 2 * t + 8]);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) mma_bf16_16816(acc2[i][j], af[i], c0, c1);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  TO* out = (TO*)a.out + (a.tiles ? 0 : (size_t)group * a.out_batch);
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm + 16 * i + g + 8 * half;
+      if (r >= rows) continue;
+      TO* o = out + (size_t)(m0 + r) * a.out_stride;
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int n = n0 + wn + 8 * j + 2 * t + e;
+          if (n >= a.N) continue;
+          float v = acc[i][j][2 * half + e];
+          if (GLU) {
+            const float gt = fminf(v, a.limit);
+            const float u = fminf(fmaxf(acc2[i][j][2 * half + e], -a.limit), a.limit);
+            v = gt * (1.0f / (1.0f + expf(-a.alpha * gt))) * (u + a.shift);
+          }
+          o[n] = from_float<TO>(v);
+        }
+    }
+}
+
+template <typename TO>
+static int launch_grouped_mma(const GroupedGemmArgs& a, dim3 grid, cudaStream_t stream) {
+  if (a.w2 != nullptr)
+    gemm_grouped_mma_kernel<TO, true><<<grid, GM_THREADS, 0, stream>>>(a);
+  else
+    gemm_grouped_mma_kernel<TO, false><<<grid, GM_THREADS, 0, stream>>>(a);
+  return llmrs_launch_status("gemm_grouped (tensor cores)");
+}
+
+// 0: the CUDA-core kernel for every product (set by tests that compare the two).
+static int g_grouped_mma = 1;
+LLMRS_API void llmrs_gemm_grouped_use_mma(int on) { g_grouped_mma = on; }
+
 template <typename TX, typename TW, typename TO>
 static int launch_grouped(const GroupedGemmArgs& a, dim3 grid, cudaStream_t stream) {
   if (a.w2 != nullptr)
@@ -161,6 +309,15 @@ LLMRS_API int llmrs_gemm_grouped(const void* x, int x_dtype, long long x_stride,
   a.limit = limit, a.alpha = alpha, a.shift = shift;
   dim3 grid((N + GG_BN - 1) / GG_BN, tiles ? max_tiles : (M + GG_BM - 1) / GG_BM, tiles ? 1 : batches);
   LLMRS_REQUIRE(grid.y >= 1 && grid.y <= 65535 && grid.z <= 65535, "gemm_grouped: too many tiles or batches");
+  // bfloat16 operands whose rows can be copied 16 bytes at a time go to the tensor cores.
+  if (g_grouped_mma && x_dtype == LLMRS_BF16 && w_dtype == LLMRS_BF16 && K % 8 == 0 && x_stride % 8 == 0 &&
+      x_batch % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && (!w2 || ((uintptr_t)w2 & 15) == 0) &&
+      (N * (long long)K) % 8 == 0) {
+    const int cols = w2 ? GmCols<true>::value : GmCols<false>::value;
+    dim3 mgrid((N + cols - 1) / cols, grid.y, grid.z);
+    return out_dtype == LLMRS_BF16 ? launch_grouped_mma<__nv_bfloat16>(a, mgrid, stream)
+                                   : launch_grouped_mma<float>(a, mgrid, stream);
+  }
   const int key = x_dtype * 4 + w_dtype * 2 + out_dtype;
   switch (key) {
     case 0: return launch_grouped<float, float, float>(a, grid, stream);

@@ -725,6 +725,14 @@ def _strides3(t: torch.Tensor, name: str):
     return t.stride(0), t.stride(1)
 
 
+def grouped_use_tensor_cores(on: bool) -> None:
+    """False: ``gemm_batched`` and ``gemm_grouped`` take the CUDA-core kernel for bfloat16 too (for tests that compare
+    the two kernels). The default is True."""
+    fn = _lib().llmrs_gemm_grouped_use_mma
+    fn.restype, fn.argtypes = None, [ctypes.c_int]
+    fn(1 if on else 0)
+
+
 def gemm_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, round_x: bool = False) -> torch.Tensor:
     """``out[m, b, :] = w[b] @ x[m, b, :]`` for x [M, B, K] and out [M, B, N] (any row and batch strides) and
     w [B, N, K] contiguous: the heads of a tensor as batches, without a copy. float32 accumulation on the CUDA
@@ -852,11 +860,24 @@ def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], latent_norm_w, 
         rot_dims, rank, ctypes.c_float(eps), _stream()), "latent_prepare")
 
 
+def latent_attention_splits(n_tokens: int, n_heads: int, span: int, sms: int):
+    """(splits, keys per split) for a step of ``n_tokens`` whose tokens see at most ``span`` keys: few tokens (decoding)
+    cut their keys so that the blocks fill the device about twice, at 64 keys or more each; many tokens are not cut."""
+    blocks = n_tokens * -(-n_heads // (4 if n_heads >= 4 else 1))
+    splits = min(max(1, (2 * sms) // max(blocks, 1)), max(1, span // 64))
+    if splits <= 1:
+        return 1, 0
+    keys = -(-(-(-span // splits)) // 16) * 16
+    return -(-span // keys), keys
+
+
 def latent_attention(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cache: torch.Tensor, table, ctx,
                      out: torch.Tensor, n_heads: int, dn: int, dr: int, rank: int, page_size: int, window: int,
-                     scale: float) -> torch.Tensor:
+                     scale: float, splits: int = 1, split_keys: int = 0) -> torch.Tensor:
     """Attention over cached latent rows with folded queries ``qa`` [tokens, heads, rank]; ``q`` the rotated
-    projected queries, ``gate`` the raw per-head gates [tokens, heads]; ``out`` [tokens, heads, rank] (any strides)."""
+    projected queries, ``gate`` the raw per-head gates [tokens, heads]; ``out`` [tokens, heads, rank] (any strides).
+    ``splits`` > 1 cuts every token's visible keys into that many runs of ``split_keys`` (which must cover the longest
+    visible span) that separate blocks take; a second kernel merges them."""
     _need(qa, "qa", contiguous=False)
     _need(q, "q", qa.dtype, contiguous=False)
     _need(gate, "gate", qa.dtype, contiguous=False)
@@ -864,9 +885,15 @@ def latent_attention(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cach
     _need(out, "out", qa.dtype, contiguous=False)
     qs, qh = _strides3(qa, "qa")
     os_, oh = _strides3(out, "out")
+    partial = None
+    if splits > 1:
+        n_floats = qa.size(0) * n_heads * splits * (rank + 2)
+        partial = ctx.scratch("latent_attention", n_floats) if hasattr(ctx, "scratch") else torch.empty(
+            (n_floats,), dtype=torch.float32, device=qa.device)
     _check(_lib().llmrs_latent_attention(
         _ptr(qa), _LL(qs), _LL(qh), _ptr(q), _LL(_row_stride(q, "q")), dn, dn + dr, _ptr(gate),
         _LL(_row_stride(gate, "gate")), _ptr(cache), dtype_code(qa.dtype), _ptr(table), table.size(1),
         _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(out), _LL(os_), _LL(oh), qa.size(0), n_heads, rank, dr,
-        page_size, window, ctypes.c_float(scale), _stream()), "latent_attention")
+        page_size, window, ctypes.c_float(scale), splits, split_keys, _ptr(partial), _stream()), "latent_attention",
+        2 if splits > 1 else 1)
     return out

@@ -122,8 +122,12 @@ class LatentAttention(Mixer):
         qa = torch.empty((T, nh, rank), dtype=proj.dtype, device=proj.device)
         ops.gemm_batched(q3[:, :, :dn], self.w_uk_t, qa)
         lat = torch.empty((T, nh, rank), dtype=proj.dtype, device=proj.device)
+        # Steps of few tokens cut the visible keys over several blocks. The span is what the step's shape implies (the
+        # window, else what the block table can hold), not the requests' lengths: a captured step replays it.
+        span = self.window if self.window > 0 else cache.block_table.size(1) * cache.page_size
+        splits, split_keys = ops.latent_attention_splits(T, nh, span, ops.sm_count(proj.device))
         ops.latent_attention(qa, q, gate, pages, cache.block_table, ctx, lat, nh, dn, dr, rank, cache.page_size,
-                             self.window, self.scale)
+                             self.window, self.scale, splits=splits, split_keys=split_keys)
         out = torch.empty((T, nh, self.vdim), dtype=proj.dtype, device=proj.device)
         ops.gemm_batched(lat, self.w_uv, out)
         return self.o_proj.forward(out.view(T, nh * self.vdim))

@@ -23,8 +23,8 @@ class MixtureOfExperts(FeedForward):
     grouping of rows by expert, the two grouped products and the weighted sum do not depend on which router ran.
 
     The rows are sorted by expert so that a tile of rows shares one expert's weights; the first product has the gated
-    unit as its epilogue. ``forward`` reads the float32 residual stream itself (``reads_residual``): its rows are
-    rounded to the activation type as they are loaded. Tensor names: ``<prefix>e<i>.gate|up|down`` and
+    unit as its epilogue; bfloat16 products run on the tensor cores (``csrc/gemm_grouped.cu``). ``forward`` takes the
+    float32 residual stream itself (``reads_residual``) and rounds its rows to the activation type. Tensor names: ``<prefix>e<i>.gate|up|down`` and
     ``<prefix>table`` unless ``names`` renames the roles."""
 
     reads_residual = True
@@ -77,11 +77,11 @@ class MixtureOfExperts(FeedForward):
         expert_of, weight_of = ops.moe_route_table(ctx.token_ids, self.table, self.n_experts)
         row_of, src_token, tiles, n_tiles = ops.moe_sort(expert_of, self.top, self.n_experts)
         n_rows = expert_of.numel()
-        bf16 = self.act_dtype == torch.bfloat16
+        if self.act_dtype == torch.bfloat16 and x.dtype == torch.float32:
+            x = ops.token_shift(x, None, None, None, torch.bfloat16)     # the rows as activations: the tensor cores' type
         act = torch.empty((n_rows, self.expert_size), dtype=self.act_dtype, device=x.device)
-        ops.gemm_grouped(x, self.w_gate, act, tiles, n_tiles, src_token, w2=self.w_up,
-                         round_x=bf16 and x.dtype == torch.float32, limit=self.limit, alpha=self.alpha,
-                         shift=self.up_shift)
+        ops.gemm_grouped(x, self.w_gate, act, tiles, n_tiles, src_token, w2=self.w_up, limit=self.limit,
+                         alpha=self.alpha, shift=self.up_shift)
         rows = torch.empty((n_rows, self.hidden_size), dtype=torch.float32, device=x.device)
         ops.gemm_grouped(act, self.w_down, rows, tiles, n_tiles, None)
         return ops.moe_combine(rows, row_of, weight_of, self.top)

@@ -114,6 +114,30 @@ def test_norm_on_a_branch_output_and_soft_cap():
     assert (got.double() - 7.5 * torch.tanh(z.double() / 7.5)).abs().max().item() < 1e-5
 
 
+@pytest.mark.parametrize("tensor_cores", [True, False])
+@pytest.mark.parametrize("M,B,N,K,pad", [(70, 3, 40, 24, 0), (5, 2, 200, 64, 8), (130, 1, 136, 72, 16), (33, 4, 50, 20, 3)])
+def test_batched_product_over_heads(M, B, N, K, pad, tensor_cores):
+    """``out[m, b] = w[b] @ x[m, b]`` on strided views (heads inside wider rows), bfloat16 on the tensor cores and on the
+    CUDA cores (rows that cannot be copied 16 bytes at a time take the latter by themselves), and float32."""
+    from llm_rs_b200 import ops
+    g = torch.Generator().manual_seed(M + N)
+    wide = torch.randn(M, B * (K + pad) + 8, generator=g)
+    w = torch.randn(B, N, K, generator=g) / math.sqrt(K)
+    ops.grouped_use_tensor_cores(tensor_cores)
+    try:
+        for dtype in (torch.bfloat16, torch.float32):
+            xw, wd = wide.to(DEV, dtype), w.to(DEV, dtype)
+            x = xw[:, : B * (K + pad)].unflatten(1, (B, K + pad))[:, :, :K]
+            out = torch.zeros(M, B, N + 8, dtype=dtype, device=DEV)
+            ops.gemm_batched(x, wd, out[:, :, :N])
+            want = torch.einsum("mbk,bnk->mbn", x.double(), wd.double()).cpu()
+            tol = 1e-5 if dtype == torch.float32 else 0.02
+            assert (out[:, :, :N].double().cpu() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+            assert torch.all(out[:, :, N:] == 0)
+    finally:
+        ops.grouped_use_tensor_cores(True)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,n_tokens", [(4, 2, 50), (3, 3, 7), (1, 1, 5), (37, 4, 300), (8, 1, 1)])
 def test_mixture_of_experts_against_plain(dtype, experts, top, n_tokens):
