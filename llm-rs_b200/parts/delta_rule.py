@@ -35,8 +35,8 @@ class GeneralDelta(Mixer):
 
     def __init__(self, hidden_size: int, n_heads: int, dim: int, decay_rank: int, norm_eps: float = 1e-6,
                  key_eps: float = 1e-6, decay_scale: float = math.exp(-0.5), names=None, prefix: str = ""):
-        if dim > 128:
-            raise ValueError(f"heads of {dim} channels: the recurrence kernel takes at most 128")
+        if dim > 256:
+            raise ValueError(f"heads of {dim} channels: the recurrence kernel takes at most 256")
         self.hidden_size, self.n_heads, self.dim, self.decay_rank = hidden_size, n_heads, dim, decay_rank
         self.norm_eps, self.key_eps, self.decay_scale = float(norm_eps), float(key_eps), float(decay_scale)
         self.prefix = prefix

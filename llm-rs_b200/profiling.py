@@ -77,10 +77,11 @@ def _cost_rows(*tensors_from):
 def _cost_grouped(x, w, out, tiles, n_tiles, src, w2=None, **k):
     rows, (G, N, K) = out.size(0), w.shape
     both = 2 if w2 is not None else 1
-    # Every expert's weights are read at least once when at least that many rows are there; the rows read and written.
-    touched = min(G, max(rows, 1))
+    # The weights of the experts that got a row are read at least once (rows dealt evenly: G (1 - (1 - 1/G)^rows) of
+    # them in expectation); the rows are read and written.
+    touched = G * (1.0 - (1.0 - 1.0 / G) ** max(rows, 1))
     return (f"{G}x{N}x{K}{' gated' if w2 is not None else ''}",
-            touched * N * K * w.element_size() * both + rows * (K * x.element_size() + N * out.element_size()),
+            int(touched * N * K * w.element_size() * both) + rows * (K * x.element_size() + N * out.element_size()),
             2.0 * rows * N * K * both)
 
 

@@ -183,7 +183,7 @@ def test_mixture_of_experts_against_plain(dtype, experts, top, n_tokens):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,d,rank", [(2, 16, 4), (1, 48, 7), (3, 64, 16), (1, 128, 8), (2, 100, 8)])
+@pytest.mark.parametrize("heads,d,rank", [(2, 16, 4), (1, 48, 7), (3, 64, 16), (1, 128, 8), (2, 100, 8), (1, 200, 8)])
 def test_delta_rule_mixer_against_plain(dtype, heads, d, rank):
     """The mixer part alone: three requests in one step (a long portion, a short one, a single token), then each
     continued from its state; slots in another order than the requests."""
