@@ -898,3 +898,34 @@ def latent_attention(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cach
         page_size, window, ctypes.c_float(scale), splits, split_keys, _ptr(partial), _stream()), "latent_attention",
         2 if splits > 1 else 1)
     return out
+
+
+def latent_prefill_tile_tokens(n_heads: int) -> int:
+    """Tokens per tile of ``latent_attention_prefill`` for a number of heads."""
+    return 4 if n_heads >= 4 else 16
+
+
+def latent_attention_prefill(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cache: torch.Tensor, table, ctx,
+                             tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int, dn: int, dr: int,
+                             rank: int, page_size: int, window: int, scale: float) -> bool:
+    """``latent_attention`` for prompt portions in bfloat16 on the tensor cores. ``tiles`` int32 [n_tiles, 2]: first
+    token of the step and number of tokens (at most ``latent_prefill_tile_tokens``) of consecutive tokens of one
+    request. Returns False, having launched nothing, when the sizes do not fit the kernel (rank % 64, rot % 16,
+    pages of a multiple of 16 keys): the caller then takes ``latent_attention``."""
+    _need(qa, "qa", torch.bfloat16, contiguous=False)
+    _need(q, "q", torch.bfloat16, contiguous=False)
+    _need(gate, "gate", torch.bfloat16, contiguous=False)
+    _need(cache, "cache", torch.bfloat16)
+    _need(out, "out", torch.bfloat16, contiguous=False)
+    _need(tiles, "tiles", torch.int32)
+    qs, qh = _strides3(qa, "qa")
+    os_, oh = _strides3(out, "out")
+    rc = _lib().llmrs_latent_attention_prefill(
+        _ptr(qa), _LL(qs), _LL(qh), _ptr(q), _LL(_row_stride(q, "q")), dn, dn + dr, _ptr(gate),
+        _LL(_row_stride(gate, "gate")), _ptr(cache), _ptr(table), table.size(1), _ptr(ctx.positions),
+        _ptr(ctx.token_req), _ptr(tiles), n_tiles, _ptr(out), _LL(os_), _LL(oh), n_heads, rank, dr, page_size, window,
+        ctypes.c_float(scale), _stream())
+    if rc == -2:
+        return False
+    _check(rc, "latent_attention_prefill")
+    return True

@@ -1,15 +1,36 @@
 """Latent attention: all heads share one cached row per token."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
+import numpy as np
 import torch
 
 from .. import ops
-from .base import Mixer, Runtime
+from .base import Mixer, Plan, Runtime, StepInfo
 from .linear import Linear
 from .registry import register
 from .spec import CacheNeed, WeightSpec
+
+
+# Prompt portions in bfloat16 take the tensor-core kernel from this many tokens a step on; LLMRS_LATENT_MMA=0 keeps the
+# CUDA-core kernel for everything.
+_LATENT_MMA = os.environ.get("LLMRS_LATENT_MMA", "1") != "0"
+PREFILL_MIN_TOKENS = 32
+
+
+def portion_tiles(q_start, n_new, tile_tokens: int) -> np.ndarray:
+    """int32 [n, 2]: (first token of the step, tokens) of tiles of at most ``tile_tokens`` consecutive tokens that do
+    not cross a request."""
+    firsts, counts = [], []
+    for qs, n in zip(np.asarray(q_start).tolist(), np.asarray(n_new).tolist()):
+        a = np.arange(0, n, tile_tokens, dtype=np.int32)
+        firsts.append(qs + a)
+        counts.append(np.minimum(tile_tokens, n - a))
+    if not firsts:
+        return np.zeros((0, 2), np.int32)
+    return np.stack([np.concatenate(firsts), np.concatenate(counts)], axis=1).astype(np.int32)
 
 
 @register("mixer", "latent_attention")
@@ -99,6 +120,30 @@ class LatentAttention(Mixer):
         return CacheNeed("window" if self.cache_window > 0 else "full", 1, self.rank, self.cache_window,
                          planes=(self.rank, self.rot_dim))
 
+    # -- the step's plan: tiles of a prompt's tokens for the tensor-core kernel -------------------------------------
+    def plan_key(self):
+        return ("latent_attention_tiles", ops.latent_prefill_tile_tokens(self.n_heads))
+
+    def plan(self, step: StepInfo) -> Plan:
+        """Steps that bring a prompt's portion are cut into tiles of tokens (none for steps of single tokens, which
+        the CUDA-core kernel takes with its keys cut over blocks, and which may be replayed from a graph)."""
+        if step.for_graph or step.n_tokens < PREFILL_MIN_TOKENS or int(np.max(step.n_new, initial=0)) <= 1:
+            return Plan(arrays={"tiles": np.zeros((0, 2), np.int32)}, values={"n_tiles": 0})
+        tiles = portion_tiles(step.q_start, step.n_new, ops.latent_prefill_tile_tokens(self.n_heads))
+        return Plan(arrays={"tiles": tiles}, values={"n_tiles": int(tiles.shape[0])})
+
+    def _tiles(self, ctx):
+        """(device tiles, how many) for this step; None when the step has no plan of them."""
+        if hasattr(ctx, "plan"):
+            view = ctx.plan(self.plan_key())
+            return (view.arrays["tiles"], view.values["n_tiles"]) if view.values["n_tiles"] else None
+        # Called outside the step function (a part alone): plan here, from the device's arrays.
+        n_new = ctx.n_new.cpu().numpy()
+        if ctx.n_tokens < PREFILL_MIN_TOKENS or int(n_new.max(initial=0)) <= 1:
+            return None
+        tiles = portion_tiles(ctx.q_start.cpu().numpy(), n_new, ops.latent_prefill_tile_tokens(self.n_heads))
+        return torch.from_numpy(tiles).to(ctx.n_new.device), int(tiles.shape[0])
+
     def forward(self, x, ctx, cache):
         nh, dn, dr, rank = self.n_heads, self.dim, self.rot_dim, self.rank
         if cache.owns == self.shares_cache:
@@ -122,6 +167,13 @@ class LatentAttention(Mixer):
         qa = torch.empty((T, nh, rank), dtype=proj.dtype, device=proj.device)
         ops.gemm_batched(q3[:, :, :dn], self.w_uk_t, qa)
         lat = torch.empty((T, nh, rank), dtype=proj.dtype, device=proj.device)
+        tiles = self._tiles(ctx) if _LATENT_MMA and proj.dtype == torch.bfloat16 else None
+        if tiles is not None and ops.latent_attention_prefill(
+                qa, q, gate, pages, cache.block_table, ctx, tiles[0], tiles[1], lat, nh, dn, dr, rank, cache.page_size,
+                self.window, self.scale):
+            out = torch.empty((T, nh, self.vdim), dtype=proj.dtype, device=proj.device)
+            ops.gemm_batched(lat, self.w_uv, out)
+            return self.o_proj.forward(out.view(T, nh * self.vdim))
         # Steps of few tokens cut the visible keys over several blocks. The span is what the step's shape implies (the
         # window, else what the block table can hold), not the requests' lengths: a captured step replays it.
         span = self.window if self.window > 0 else cache.block_table.size(1) * cache.page_size

@@ -101,6 +101,11 @@ def _cost_latent_attention(qa, q, gate, cache, table, ctx, out, n_heads, dn, dr,
             lambda: 2.0 * float(pairs) * n_heads * (2 * rank + dr))
 
 
+def _cost_latent_prefill(qa, q, gate, cache, table, ctx, tiles, n_tiles, out, n_heads, dn, dr, rank, page_size, window,
+                         scale, **k):
+    return _cost_latent_attention(qa, q, gate, cache, table, ctx, out, n_heads, dn, dr, rank, page_size, window, scale)
+
+
 def _cost_delta_rule(r, k, v, gate, a_raw, decay_raw, decay_bias, a_bias, norm_w, state, ctx, n_heads, d, *a, **kw):
     tokens = r.size(0)
     return (f"{tokens} tokens", tokens * n_heads * d * (6 * r.element_size() + 4) + 2 * ctx.n_requests * n_heads * d * d * 4,
@@ -109,6 +114,7 @@ def _cost_delta_rule(r, k, v, gate, a_raw, decay_raw, decay_bias, a_bias, norm_w
 
 WRAPPED: Dict[str, Callable] = {
     "gemm_grouped": _cost_grouped, "gemm_batched": _cost_batched, "latent_attention": _cost_latent_attention,
+    "latent_attention_prefill": _cost_latent_prefill,
     "delta_rule": _cost_delta_rule, "token_shift": _cost_rows(0), "outnorm_add": _cost_rows(0, 1),
     "latent_prepare": _cost_rows(0), "tanh_slice": _cost_rows(0), "softcap_": _cost_rows(0),
     "moe_route_table": _cost_rows(0), "moe_sort": _cost_rows(0), "moe_combine": _cost_rows(0),
