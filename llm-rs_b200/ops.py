@@ -833,12 +833,12 @@ def delta_rule(r, k, v, gate, a_raw, decay_raw, decay_bias, a_bias, norm_w, stat
     _need(decay_raw, "decay_raw", torch.float32)
     _need(state, "state", torch.float32)
     out = torch.empty((r.size(0), n_heads * d), dtype=r.dtype, device=r.device)
-    o_raw = torch.empty((r.size(0), n_heads * d), dtype=torch.float32, device=r.device)
+    work = torch.empty((7 * r.size(0) * n_heads * d,), dtype=torch.float32, device=r.device)     # six prepared rows and o
     _check(_lib().llmrs_delta_rule(
         _ptr(r), _ptr(k), _ptr(v), _ptr(gate), _ptr(a_raw), _LL(stride), dtype_code(r.dtype), _ptr(decay_raw),
         _ptr(decay_bias), _ptr(a_bias), _ptr(norm_w), _ptr(state), _ptr(ctx.q_start), _ptr(ctx.n_new),
-        _ptr(ctx.slot_ids), _ptr(o_raw), _ptr(out), r.size(0), ctx.n_requests, n_heads, d, ctypes.c_float(decay_scale),
-        ctypes.c_float(key_eps), ctypes.c_float(norm_eps), _stream()), "delta_rule", 2)
+        _ptr(ctx.slot_ids), _ptr(work), _ptr(out), r.size(0), ctx.n_requests, n_heads, d, ctypes.c_float(decay_scale),
+        ctypes.c_float(key_eps), ctypes.c_float(norm_eps), _stream()), "delta_rule", 3)
     return out
 
 
