@@ -261,6 +261,191 @@ static int launch_latent(int maxc, dim3 grid, size_t smem, cudaStream_t stream, 
   return llmrs_launch_status("latent_attention (merge)");
 }
 
+// ---------------------------------------------------------------------------------
+// Steps of few tokens (decoding): the same attention with the work laid out for latency. A warp takes 32 keys at a
+// time. Scores: a lane per key walks its key's cached row in 16-byte loads against the queries of the group's heads,
+// which lie in shared memory (read as broadcasts): no reduction across lanes. Values: a lane per 16-byte piece of the
+// latent; the key's weight comes by shuffle, its row is read in straight 16-byte loads. The online softmax advances
+// once per 32 keys. Every block leaves its partial result for the merge kernel. Needs rank and rot to be multiples of
+// 16 bytes' worth of elements.
+// ---------------------------------------------------------------------------------
+template <typename TA> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x, v[1] = x.y, v[2] = x.z, v[3] = x.w;
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 x = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+  }
+};
+
+template <typename TA, int HG, int NV>      // NV: 16-byte pieces of the latent per lane (rank <= 32 * NV * Vec16::N)
+__global__ void __launch_bounds__(LA_WARPS * 32)
+latent_decode_kernel(const TA* __restrict__ qa, long long qa_token, long long qa_head, const TA* __restrict__ q,
+                     long long q_stride, int q_rot_at, int q_head_width, const TA* __restrict__ cache,
+                     const int* __restrict__ table, int table_width, const int* __restrict__ positions,
+                     const int* __restrict__ token_req, int n_heads, int rank, int dr, int page_size, int window,
+                     float scale, int split_keys, float* __restrict__ partial) {
+  constexpr int VN = Vec16<TA>::N;
+  extern __shared__ __align__(16) float sm[];
+  const int KD = rank + dr;
+  float* s_q = sm;                                          // [HG][KD]: folded query, then the rotated part
+  float* s_m = s_q + HG * KD;                               // [warps][HG]
+  float* s_l = s_m + LA_WARPS * HG;                         // [warps][HG]
+  float* s_acc = s_l + LA_WARPS * HG;                       // [warps][HG][rank]
+  const int t = blockIdx.x, h0 = blockIdx.y * HG;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = positions[t];
+  const int* tab = table + (size_t)token_req[t] * table_width;
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  lo += blockIdx.z * split_keys;
+  const int hi = min(pos, lo + split_keys - 1);
+  for (int e = threadIdx.x; e < HG * KD; e += blockDim.x) {
+    const int g = e / KD, c = e % KD, h = min(h0 + g, n_heads - 1);
+    s_q[e] = c < rank ? to_float(qa[(size_t)t * qa_token + (size_t)h * qa_head + c])
+                      : to_float(q[(size_t)t * q_stride + (size_t)h * q_head_width + q_rot_at + (c - rank)]);
+  }
+  __syncthreads();
+  const size_t page_elems = (size_t)page_size * KD;
+  float acc[HG][NV * VN], m[HG], l[HG];
+#pragma unroll
+  for (int g = 0; g < HG; ++g) {
+    m[g] = -INFINITY, l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV * VN; ++i) acc[g][i] = 0.f;
+  }
+  for (int base = lo + 32 * warp; base <= hi; base += 32 * LA_WARPS) {
+    const int j = base + lane;
+    const bool live = j <= hi;
+    const int jj = live ? j : hi;                           // idle lanes walk a real row and are masked afterwards
+    int page = tab[jj / page_size];
+    page = LLMRS_CHECKED_PAGE(page, 3, jj);
+    const long long c_off = (long long)page * page_elems + (long long)(jj % page_size) * rank;
+    const TA* crow = cache + c_off;
+    const TA* rrow = cache + (size_t)page * page_elems + (size_t)page_size * rank + (size_t)(jj % page_size) * dr;
+    float sc[HG];
+#pragma unroll
+    for (int g = 0; g < HG; ++g) sc[g] = 0.f;
+    for (int c = 0; c < KD; c += VN) {
+      float kv[VN];
+      Vec16<TA>::load(c < rank ? crow + c : rrow + (c - rank), kv);
+#pragma unroll
+      for (int g = 0; g < HG; ++g) {
+        const float* qg = s_q + g * KD + c;
+#pragma unroll
+        for (int e = 0; e < VN; e += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qg + e);
+          sc[g] = fmaf(q4.x, kv[e], fmaf(q4.y, kv[e + 1], fmaf(q4.z, kv[e + 2], fmaf(q4.w, kv[e + 3], sc[g]))));
+        }
+      }
+    }
+    float pw[HG], corr[HG];
+#pragma unroll
+    for (int g = 0; g < HG; ++g) {
+      const float sv = live ? sc[g] * scale : -INFINITY;
+      const float m_new = fmaxf(m[g], warp_max(sv));        // lane 0's key always exists: finite
+      corr[g] = expf(m[g] - m_new);
+      pw[g] = live ? expf(sv - m_new) : 0.f;
+      l[g] = l[g] * corr[g] + warp_sum(pw[g]);
+      m[g] = m_new;
+#pragma unroll
+      for (int i = 0; i < NV * VN; ++i) acc[g][i] *= corr[g];
+    }
+    const int n_live = min(32, hi - base + 1);
+    for (int k = 0; k < n_live; ++k) {
+      const long long off = __shfl_sync(0xffffffffu, c_off, k);
+      float pk[HG];
+#pragma unroll
+      for (int g = 0; g < HG; ++g) pk[g] = __shfl_sync(0xffffffffu, pw[g], k);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = (i * 32 + lane) * VN;
+        if (c < rank) {
+          float cv[VN];
+          Vec16<TA>::load(cache + off + c, cv);
+#pragma unroll
+          for (int g = 0; g < HG; ++g)
+#pragma unroll
+            for (int e = 0; e < VN; ++e) acc[g][i * VN + e] = fmaf(pk[g], cv[e], acc[g][i * VN + e]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < HG; ++g) {
+    if (lane == 0) s_m[warp * HG + g] = m[g], s_l[warp * HG + g] = l[g];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * VN;
+      if (c < rank)
+#pragma unroll
+        for (int e = 0; e < VN; ++e) s_acc[(size_t)(warp * HG + g) * rank + c + e] = acc[g][i * VN + e];
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < HG * rank; e += blockDim.x) {
+    const int g = e / rank, c = e % rank;
+    if (h0 + g >= n_heads) continue;
+    float mm = -INFINITY;
+    for (int w = 0; w < LA_WARPS; ++w) mm = fmaxf(mm, s_m[w * HG + g]);
+    float num = 0.f, den = 0.f;
+    for (int w = 0; w < LA_WARPS; ++w) {
+      const float mw = s_m[w * HG + g];
+      if (mw == -INFINITY) continue;                // a warp that saw no key
+      const float f = expf(mw - mm);
+      num = fmaf(f, s_acc[(size_t)(w * HG + g) * rank + c], num);
+      den = fmaf(f, s_l[w * HG + g], den);
+    }
+    float* p = partial + (((size_t)t * n_heads + h0 + g) * gridDim.z + blockIdx.z) * (rank + 2);
+    p[c] = num;
+    if (c == 0) p[rank] = mm, p[rank + 1] = den;
+  }
+}
+
+// Launches the kernel above when the sizes allow it (returns false otherwise, having launched nothing).
+template <typename TA>
+static bool try_latent_decode(int* rc, dim3 grid, cudaStream_t stream, const void* qa, long long qa_token,
+                              long long qa_head, const void* q, long long q_stride, int q_rot_at, int q_head_width,
+                              const void* cache, const int* table, int table_width, const int* positions,
+                              const int* token_req, int n_heads, int rank, int dr, int page_size, int window,
+                              float scale, int split_keys, float* partial) {
+  constexpr int VN = Vec16<TA>::N;
+  const int hg = n_heads >= 4 ? 4 : 1;
+  if (rank % VN || dr % VN || rank > 512 || ((uintptr_t)cache & 15) || (rank + dr) % 4) return false;
+  const int pieces = (rank / VN + 31) / 32;                 // 16-byte pieces of the latent per lane
+  if (pieces > 4 || pieces * VN * hg > 64) return false;    // at most 64 accumulators a lane
+  const size_t smem = ((size_t)hg * (rank + dr) + 2 * LA_WARPS * hg + (size_t)LA_WARPS * hg * rank) * sizeof(float);
+  if (smem > 48 * 1024) return false;
+#define LLMRS_LD(HG_, NV_)                                                                                          \
+  latent_decode_kernel<TA, HG_, NV_><<<grid, LA_WARPS * 32, smem, stream>>>(                                        \
+      (const TA*)qa, qa_token, qa_head, (const TA*)q, q_stride, q_rot_at, q_head_width, (const TA*)cache, table,     \
+      table_width, positions, token_req, n_heads, rank, dr, page_size, window, scale, split_keys, partial)
+  if (hg == 4) {
+    if (pieces == 1) LLMRS_LD(4, 1);
+    else if (pieces == 2) LLMRS_LD(4, 2);
+    else if (VN == 4) LLMRS_LD(4, 4);
+    else return false;
+  } else {
+    if (pieces == 1) LLMRS_LD(1, 1);
+    else if (pieces == 2) LLMRS_LD(1, 2);
+    else LLMRS_LD(1, 4);
+  }
+#undef LLMRS_LD
+  *rc = llmrs_launch_status("latent_attention (few tokens)");
+  return true;
+}
+
 // qa: folded queries [tokens, heads, rank] with strides; q: the projected queries, head h's rotated part at
 // q + t * q_stride + h * q_head_width + q_rot_at; gate: raw gate values [tokens, heads] (row stride given);
 // out: [tokens, heads, rank] with strides. n_splits > 1: every (token, head group) is cut into n_splits blocks of
@@ -272,7 +457,7 @@ LLMRS_API int llmrs_latent_attention(const void* qa, long long qa_token, long lo
                                      int table_width, const int* positions, const int* token_req, void* out,
                                      long long out_token, long long out_head, int n_tokens, int n_heads, int rank,
                                      int dr, int page_size, int window, float scale, int n_splits, int split_keys,
-                                     float* partial, cudaStream_t stream) {
+                                     float* partial, int few_tokens, cudaStream_t stream) {
   LLMRS_REQUIRE(n_tokens >= 0 && n_heads > 0 && rank > 0 && dr > 0 && page_size > 0, "latent_attention: bad sizes");
   LLMRS_REQUIRE(rank <= 512, "latent_attention: a latent of at most 512, got %d", rank);
   LLMRS_REQUIRE(window >= 0, "latent_attention: bad window");
@@ -283,9 +468,31 @@ LLMRS_API int llmrs_latent_attention(const void* qa, long long qa_token, long lo
   LLMRS_REQUIRE(smem <= 48 * 1024, "latent_attention: sizes need %zu bytes of shared memory", smem);
   LLMRS_REQUIRE(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || (split_keys > 0 && partial != nullptr)),
                 "latent_attention: bad split");
-  if (n_splits == 1) partial = nullptr;
   dim3 grid(n_tokens, (n_heads + hg - 1) / hg, n_splits);
   LLMRS_REQUIRE(grid.y <= 65535, "latent_attention: too many heads");
+  if (few_tokens && partial != nullptr && split_keys > 0) {
+    // The kernel laid out for latency; it always leaves partial results, which the merge kernel finishes.
+    int rc = 0;
+    bool done = false;
+#define LLMRS_LD_ARGS                                                                                              \
+  &rc, grid, stream, qa, qa_token, qa_head, q, q_stride, q_rot_at, q_head_width, cache, table, table_width,        \
+      positions, token_req, n_heads, rank, dr, page_size, window, scale, split_keys, partial
+    if (dtype == LLMRS_F32) done = try_latent_decode<float>(LLMRS_LD_ARGS);
+    else if (dtype == LLMRS_BF16) done = try_latent_decode<__nv_bfloat16>(LLMRS_LD_ARGS);
+#undef LLMRS_LD_ARGS
+    if (done) {
+      if (rc != 0) return rc;
+      if (dtype == LLMRS_F32)
+        latent_combine_kernel<float><<<dim3(n_tokens, n_heads), 128, 0, stream>>>(
+            partial, (const float*)gate, gate_stride, (float*)out, out_token, out_head, n_heads, rank, n_splits);
+      else
+        latent_combine_kernel<__nv_bfloat16><<<dim3(n_tokens, n_heads), 128, 0, stream>>>(
+            partial, (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_token, out_head, n_heads, rank,
+            n_splits);
+      return llmrs_launch_status("latent_attention (merge)");
+    }
+  }
+  if (n_splits == 1) partial = nullptr;
 #define LLMRS_LA_ARGS                                                                                              \
   maxc, grid, smem, stream, qa, qa_token, qa_head, q, q_stride, q_rot_at, q_head_width, gate, gate_stride, cache,  \
       table, table_width, positions, token_req, out, out_token, out_head, n_heads, rank, dr, page_size, window, scale, \

@@ -861,6 +861,9 @@ def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], latent_norm_w, 
         rot_dims, rank, ctypes.c_float(eps), _stream()), "latent_prepare")
 
 
+LATENT_FEW_TOKENS = 64      # steps of at most this many tokens take the latent attention kernel laid out for latency
+
+
 def latent_attention_splits(n_tokens: int, n_heads: int, span: int, sms: int):
     """(splits, keys per split) for a step of ``n_tokens`` whose tokens see at most ``span`` keys: few tokens (decoding)
     cut their keys so that the blocks fill the device about twice, at 64 keys or more each; many tokens are not cut."""
@@ -887,7 +890,10 @@ def latent_attention(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cach
     qs, qh = _strides3(qa, "qa")
     os_, oh = _strides3(out, "out")
     partial = None
-    if splits > 1:
+    few = qa.size(0) <= LATENT_FEW_TOKENS       # the kernel laid out for latency always leaves partial results
+    if few and splits <= 1:
+        splits, split_keys = 1, 1 << 29
+    if splits > 1 or few:
         n_floats = qa.size(0) * n_heads * splits * (rank + 2)
         partial = ctx.scratch("latent_attention", n_floats) if hasattr(ctx, "scratch") else torch.empty(
             (n_floats,), dtype=torch.float32, device=qa.device)
@@ -895,8 +901,8 @@ def latent_attention(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cach
         _ptr(qa), _LL(qs), _LL(qh), _ptr(q), _LL(_row_stride(q, "q")), dn, dn + dr, _ptr(gate),
         _LL(_row_stride(gate, "gate")), _ptr(cache), dtype_code(qa.dtype), _ptr(table), table.size(1),
         _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(out), _LL(os_), _LL(oh), qa.size(0), n_heads, rank, dr,
-        page_size, window, ctypes.c_float(scale), splits, split_keys, _ptr(partial), _stream()), "latent_attention",
-        2 if splits > 1 else 1)
+        page_size, window, ctypes.c_float(scale), splits, split_keys, _ptr(partial), int(few), _stream()),
+        "latent_attention", 2 if partial is not None else 1)
     return out
 
 

@@ -183,7 +183,7 @@ def test_mixture_of_experts_against_plain(dtype, experts, top, n_tokens):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,d,rank", [(2, 16, 4), (1, 48, 7), (3, 64, 16), (1, 128, 8), (2, 100, 8), (1, 200, 8)])
+@pytest.mark.parametrize("heads,d,rank", [(2, 16, 4), (1, 48, 7), (3, 64, 16), (1, 128, 8), (2, 100, 8), (1, 200, 8), (2, 30, 4), (1, 7, 3)])
 def test_delta_rule_mixer_against_plain(dtype, heads, d, rank):
     """The mixer part alone: three requests in one step (a long portion, a short one, a single token), then each
     continued from its state; slots in another order than the requests."""
@@ -244,7 +244,8 @@ def _latent_setup(dtype, heads, dn, dr, dv, rank, window, rot_dims, page_size, n
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,dn,dr,dv,rank,window,rot_dims,page", [
     (4, 16, 8, 24, 40, 20, 8, 16), (1, 24, 16, 40, 50, 0, 8, 8), (5, 8, 32, 8, 100, 7, 32, 4),
-    (8, 32, 32, 32, 128, 130, 32, 16), (3, 64, 64, 16, 300, 64, 64, 64)])
+    (8, 32, 32, 32, 128, 130, 32, 16), (3, 64, 64, 16, 300, 64, 64, 64), (3, 16, 16, 16, 64, 24, 16, 16),
+    (5, 32, 16, 32, 128, 50, 16, 32), (2, 8, 4, 8, 12, 9, 4, 16)])
 def test_latent_attention_mixer_against_plain(dtype, heads, dn, dr, dv, rank, window, rot_dims, page):
     """The mixer part alone over scattered pages: a prompt portion, then the rest in portions and single tokens,
     beside a second request in the same steps; windows shorter and longer than a page, none at all."""
