@@ -58,8 +58,28 @@ RUSADRA_C = {
         (_delta(4, 64, 16), _moe(128, 1.0, 8, 2)),
         (_latent(8, 32, 32, 32, 128, 130, base=1e6, kv_from=0), _moe(64, 1.0, 8, 2)))}
 
+# Recurrent layers only: the model asks for no pages at all, only state. One head of 16 channels, one expert out of
+# one, a layer without feed-forward.
+RUSADRA_D = {
+    "architecture": "Rusadra", "vocab": 97, "width": 48, "norm": {"eps": 1e-6}, "logit_softcap": 8.0,
+    "layers": _layers(
+        (_delta(1, 16, 3), _moe(32, 1.0, 1, 1)),
+        (_delta(3, 24, 6), None),
+        (_delta(2, 64, 9), _moe(16, 0.5, 6, 2)))}
+
+# Attention layers only, no feed-forward anywhere: one layer that owns its rows, two that read them through other
+# windows, a second owner with a window of one key (a token sees only itself).
+RUSADRA_E = {
+    "architecture": "Rusadra", "vocab": 130, "width": 64, "norm": {"eps": 1e-5},
+    "layers": _layers(
+        (_latent(4, 16, 16, 16, 64, 40, base=1e5), None),
+        (_latent(2, 32, 16, 8, 64, 17, base=1e5, kv_from=0), None),
+        (_latent(4, 8, 8, 24, 32, 1, base=50.0), None),
+        (_latent(6, 16, 16, 16, 64, 64, base=1e5, kv_from=0), None))}
+
 # name -> (config.json, seed, sigma of matrices, page size)
-RUSADRA = {"A": (RUSADRA_A, 3, 0.08, 16), "B": (RUSADRA_B, 4, 0.1, 8), "C": (RUSADRA_C, 5, 0.05, 16)}
+RUSADRA = {"A": (RUSADRA_A, 3, 0.08, 16), "B": (RUSADRA_B, 4, 0.1, 8), "C": (RUSADRA_C, 5, 0.05, 16),
+           "D": (RUSADRA_D, 6, 0.1, 16), "E": (RUSADRA_E, 7, 0.1, 16)}
 
 
 def write_rusadra_model(name: str, folder: str, dtype=torch.bfloat16) -> str:

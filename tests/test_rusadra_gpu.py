@@ -22,7 +22,8 @@ pytestmark = pytest.mark.gpu
 TOL_F32 = 2e-4          # float32 engine against float64: rounding only
 TOL_BF16_REL = 0.04     # of the largest logit; a wrong key, state or expert moves logits by their own size
 DEV = "cuda:0"
-LENGTHS = {"A": [2, 19, 40, 77, 131, 260], "B": [1, 9, 33, 70, 128, 161], "C": [5, 31, 66, 150, 300]}
+LENGTHS = {"A": [2, 19, 40, 77, 131, 260], "B": [1, 9, 33, 70, 128, 161], "C": [5, 31, 66, 150, 300],
+           "D": [1, 2, 18, 65, 140], "E": [3, 16, 47, 90, 200]}
 MODES = ["whole", "tail", "portions", "mixed"]
 
 
@@ -37,7 +38,29 @@ def models(tmp_path_factory):
         reqs = {f"r{i}": rng.integers(0, cfg["vocab"], n).tolist() for i, n in enumerate(LENGTHS[name])}
         ref = {r: P.forward(cfg, w, toks).numpy() for r, toks in reqs.items()}
         out[name] = (path, cfg, w, reqs, ref)
+        FRAGILE[name] = _fragile_positions(cfg, w, reqs, ref)
     return out
+
+
+FRAGILE = {}      # model name -> {(request, position)} that bfloat16 cannot be held to (see _fragile_positions)
+
+
+def _fragile_positions(cfg, w, reqs, ref):
+    """Positions whose logits move by more than half the bfloat16 tolerance when every matrix is disturbed by relative
+    noise of bfloat16's rounding size (2^-9), in the plain implementation itself. The design has such places by
+    construction: a recurrent head's output is divided by its own root mean square, so at a sequence's first token,
+    where it is (k . r) v, only the SIGN of k . r survives, and rounding flips it when k and r are nearly orthogonal.
+    The float32 engine is held to every position; the bfloat16 engine to all but these (a bounded share)."""
+    g = torch.Generator().manual_seed(99)
+    noisy = {k: (v * (1.0 + 2.0 ** -9 * torch.randn(v.shape, generator=g, dtype=v.dtype)) if v.is_floating_point() and v.dim() == 2
+                 else v) for k, v in w.items()}
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    fragile = set()
+    for r, toks in reqs.items():
+        moved = np.abs(P.forward(cfg, noisy, toks).numpy() - ref[r]).max(axis=1)
+        fragile |= {(r, int(p)) for p in np.nonzero(moved > 0.5 * TOL_BF16_REL * scale)[0]}
+    assert len(fragile) <= 0.2 * sum(len(t) for t in reqs.values()), "too many ill-conditioned positions for a test"
+    return fragile
 
 
 def _ctx(n_new, cached, slots=None):
@@ -51,11 +74,11 @@ def _ctx(n_new, cached, slots=None):
                            token_req=i32(token_req), positions=i32(positions))
 
 
-def _assert_logits(got, ref, dtype, what):
-    """float32: every position within TOL_F32. bfloat16: a recurrent head whose output is nearly orthogonal to its
-    query is divided by a tiny root mean square, which magnifies rounding at that one position (the float32 engine
-    shows the same positions at 20 times its usual error), so 1 % of the positions may exceed the tolerance, none
-    by more than 2.5 times; a wrong key, state or expert moves every later position by the logits' own size."""
+def _assert_logits(got, ref, dtype, what, fragile=()):
+    """float32: every position within TOL_F32. bfloat16: the positions in ``fragile`` are left out; of the others 1 %
+    may exceed the tolerance, none by more than 2.5 times (a head whose output is small against its parts magnifies
+    rounding at that one position; the float32 engine shows the same positions at 20 times its usual error). A wrong
+    key, state or expert moves every later position by the logits' own size."""
     scale = max(float(np.abs(r).max()) for r in ref.values())
     diffs = {k: float(np.abs(row.astype(np.float64) - ref[k[0]][k[1]]).max()) for k, row in got.items()}
     assert all(np.isfinite(d) for d in diffs.values()), what
@@ -64,6 +87,8 @@ def _assert_logits(got, ref, dtype, what):
         assert diffs[worst] <= TOL_F32, f"{what}: max |diff| {diffs[worst]:.3e} at {worst}"
         return
     tol = TOL_BF16_REL * scale
+    diffs = {k: d for k, d in diffs.items() if (k[0].replace("again", ""), k[1]) not in fragile}
+    worst = max(diffs, key=diffs.get)
     over = [k for k, d in diffs.items() if d > tol]
     assert diffs[worst] <= 2.5 * tol and len(over) <= max(1, len(diffs) // 100), \
         f"{what}: max |diff| {diffs[worst]:.3e} at {worst}, {len(over)} of {len(diffs)} over {tol:.3e}"
@@ -340,7 +365,7 @@ def test_replay_matches_plain(models, name, mode, dtype):
     assert [runner.manager.free_pages(g) for g in range(len(runner.manager.groups))] == free_before, "pages were lost"
     runner.check_kernels()
     assert len(got) == sum(len(t) for t in reqs.values())
-    _assert_logits(got, ref, dtype, f"{name} {mode} {dtype}")
+    _assert_logits(got, ref, dtype, f"{name} {mode} {dtype}", FRAGILE[name])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -360,7 +385,7 @@ def test_mixed_replay_with_other_cuts_and_slots_used_again(models, name, seed, d
                                         page_size=RUSADRA[name][3], max_requests=3)
     got = RU.run_steps(runner, steps)
     assert len(got) == 2 * sum(len(t) for t in reqs.values())
-    _assert_logits(got, ref2, dtype, f"{name} seed {seed} {dtype}")
+    _assert_logits(got, ref2, dtype, f"{name} seed {seed} {dtype}", FRAGILE[name])
 
 
 def test_a_far_window_and_an_all_state_model_run_beyond_the_pool(models, tmp_path):
