@@ -506,13 +506,16 @@ LLMRS_API int llmrs_latent_attention(const void* qa, long long qa_token, long lo
 
 // ---------------------------------------------------------------------------------
 // Prompt portions in bfloat16 on the tensor cores (mma.sync m16n8k16). A block takes a tile of consecutive tokens of
-// one request times a group of heads as the 16 rows of the MMA (4 tokens x 4 heads, or 16 tokens x 1 head) and
-// walks the visible keys 16 at a time. A key's cached row [latent | rotated part] is copied into shared memory once
+// one request times a group of heads as its rows, LP_MT pieces of 16 for the MMA (with two pieces: 8 tokens x 4 heads,
+// or 32 tokens x 1 head) and walks the visible keys 16 at a time. A key's cached row [latent | rotated part] is copied into shared memory once
 // (16-byte asynchronous copies, two buffers) and serves as the key operand (all rank + rot columns) and as the value
 // operand (the latent columns). The four warps split the k range of the score product, add their partial 16 x 16
 // scores through shared memory, keep the same online softmax each, and own a quarter of the latent columns of the
 // output each. Needs rank % 64 == 0, rot % 16 == 0 and pages of a multiple of 16 keys.
 // ---------------------------------------------------------------------------------
+constexpr int LP_MT = 2;                 // 16-row pieces of a block's rows (755 us against 780 with one, rank 512, 16 heads)
+constexpr int LP_ROWS = 16 * LP_MT;
+
 template <int HG, int NTV>      // NTV: 8-column pieces of the output per warp, at most (rank / 32)
 __global__ void __launch_bounds__(128)
 latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, long long qa_token, long long qa_head,
@@ -523,32 +526,35 @@ latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, long long qa_tok
                           const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, long long out_token,
                           long long out_head, int n_heads, int rank, int dr, int page_size, int window, float scale) {
   typedef __nv_bfloat16 bf16;
-  constexpr int TQ = 16 / HG;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int KD = rank + dr, LD = KD + 8;
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                   // [16][LD]
-  bf16* Ks = Qs + 16 * LD;                                        // [2][16][LD]
-  float* Sp = reinterpret_cast<float*>(Ks + 2 * 16 * LD);         // [4][16][17]
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                   // [rows][LD]
+  bf16* Ks = Qs + LP_ROWS * LD;                                   // [2][16][LD]
+  float* Sp = reinterpret_cast<float*>(Ks + 2 * 16 * LD);         // [4][rows][17]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int t0 = tiles[2 * blockIdx.x], cnt = tiles[2 * blockIdx.x + 1], h0 = blockIdx.y * HG;
   const int p_first = positions[t0], p_last = p_first + cnt - 1;
   const int* tab = table + (size_t)token_req[t0] * table_width;
 
-  for (int e = tid; e < 16 * KD; e += 128) {
-    const int r = e / KD, c = e % KD, tq = r / HG, h = h0 + r % HG;
-    bf16 v = __float2bfloat16_rn(0.f);
-    if (tq < cnt && h < n_heads)
-      v = c < rank ? qa[(size_t)(t0 + tq) * qa_token + (size_t)h * qa_head + c]
-                   : q[(size_t)(t0 + tq) * q_stride + (size_t)h * q_head_width + q_rot_at + (c - rank)];
-    Qs[r * LD + c] = v;
+  // Row r of the block is token t0 + r / HG, head h0 + r % HG. Eight threads copy a row (no division in the loops).
+  for (int r = tid >> 3; r < LP_ROWS; r += 16) {
+    const int tq = r / HG, h = h0 + r % HG;
+    const bool there = tq < cnt && h < n_heads;
+    const bf16* qa_row = qa + (size_t)(t0 + (there ? tq : 0)) * qa_token + (size_t)(there ? h : 0) * qa_head;
+    const bf16* qr_row = q + (size_t)(t0 + (there ? tq : 0)) * q_stride + (size_t)(there ? h : 0) * q_head_width + q_rot_at;
+    bf16* dst = Qs + r * LD;
+    for (int c = tid & 7; c < rank; c += 8) dst[c] = there ? qa_row[c] : __float2bfloat16_rn(0.f);
+    for (int c = tid & 7; c < dr; c += 8) dst[rank + c] = there ? qr_row[c] : __float2bfloat16_rn(0.f);
   }
-  // This lane's two rows (g and g + 8): their positions, or -1 for rows that do not exist.
-  int pos_r[2];
+  // This lane's rows (g and g + 8 of every 16-row piece): their positions, or -1 for rows that do not exist.
+  int pos_r[LP_MT][2];
 #pragma unroll
-  for (int hf = 0; hf < 2; ++hf) {
-    const int r = g + 8 * hf, tq = r / HG;
-    pos_r[hf] = (tq < cnt && h0 + r % HG < n_heads) ? p_first + tq : -1;
-  }
+  for (int mt = 0; mt < LP_MT; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int r = 16 * mt + g + 8 * hf, tq = r / HG;
+      pos_r[mt][hf] = (tq < cnt && h0 + r % HG < n_heads) ? p_first + tq : -1;
+    }
   const int lo = window > 0 ? max(0, p_first - window + 1) : 0;
   const int j_begin = (lo / 16) * 16;
   const int n_tiles = (p_last - j_begin) / 16 + 1;
@@ -558,20 +564,27 @@ latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, long long qa_tok
     const int page = tab[j0 / page_size], slot0 = j0 % page_size;
     const bf16* base = cache + (size_t)(page < 0 ? 0 : page) * page_elems;
     bf16* dst = Ks + (size_t)stage * 16 * LD;
-    for (int e = tid; e < 16 * chunks; e += 128) {
-      const int key = e / chunks, ch = e % chunks;
-      const bf16* src = ch < c_chunks ? base + (size_t)(slot0 + key) * rank + ch * 8
-                                      : base + (size_t)page_size * rank + (size_t)(slot0 + key) * dr + (ch - c_chunks) * 8;
-      cp_async_16(dst + key * LD + ch * 8, src, (page >= 0 && j0 + key <= p_last) ? 16 : 0);   // later keys: zeros
-    }
+    // Eight threads copy a key's row, 16 bytes at a time: first the latent, then the rotated part.
+    const int key = tid >> 3;
+    const bool in = page >= 0 && j0 + key <= p_last;          // later keys: zeros
+    const bf16* c_src = base + (size_t)(slot0 + key) * rank;
+    const bf16* r_src = base + (size_t)page_size * rank + (size_t)(slot0 + key) * dr;
+    bf16* row = dst + key * LD;
+    for (int ch = tid & 7; ch < c_chunks; ch += 8) cp_async_16(row + ch * 8, c_src + ch * 8, in ? 16 : 0);
+    for (int ch = tid & 7; ch < chunks - c_chunks; ch += 8) cp_async_16(row + rank + ch * 8, r_src + ch * 8, in ? 16 : 0);
     cp_async_commit();
   };
 
-  float acc[NTV][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float acc[LP_MT][NTV][4], m[LP_MT][2], l[LP_MT][2];
 #pragma unroll
-  for (int i = 0; i < NTV; ++i)
+  for (int mt = 0; mt < LP_MT; ++mt) {
+    m[mt][0] = m[mt][1] = -INFINITY;
+    l[mt][0] = l[mt][1] = 0.f;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+    for (int i = 0; i < NTV; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[mt][i][e] = 0.f;
+  }
   const int ntv = rank / 32, cw0 = warp * (rank / 4), k_steps = KD / 16;
 
   load_tile(0, j_begin);
@@ -585,68 +598,87 @@ latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, long long qa_tok
     }
     __syncthreads();
     const bf16* K = Ks + (size_t)stage * 16 * LD;
-    // Scores: this warp's share of the k range.
-    float sp[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    for (int ks = warp; ks < k_steps; ks += 4) {
-      uint32_t a[4];
-      a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * LD + ks * 16 + 2 * t);
-      a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * LD + ks * 16 + 2 * t);
-      a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * LD + ks * 16 + 2 * t + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * LD + ks * 16 + 2 * t + 8);
+    // Scores: this warp's share of the k range, for all rows.
+    float sp[LP_MT][2][4];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(K + (nt * 8 + g) * LD + ks * 16 + 2 * t);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(K + (nt * 8 + g) * LD + ks * 16 + 2 * t + 8);
-        mma_bf16_16816(sp[nt], a, b0, b1);
-      }
-    }
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) Sp[(warp * 16 + g + 8 * (e >> 1)) * 17 + nt * 8 + 2 * t + (e & 1)] = sp[nt][e];
-    __syncthreads();
-    // Every warp adds the four partial scores of its fragment positions and keeps the same softmax.
-    float p[2][4];
-    float row_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int hf = e >> 1, col = nt * 8 + 2 * t + (e & 1), j = j0 + col;
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) s += Sp[(w * 16 + g + 8 * hf) * 17 + col];
-        const bool seen = pos_r[hf] >= 0 && j <= pos_r[hf] && (window <= 0 || j > pos_r[hf] - window);
-        s = seen ? s * scale : -INFINITY;
-        p[nt][e] = s;
-        row_max[hf] = fmaxf(row_max[hf], s);
-      }
-    float corr[2];
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      row_max[hf] = fmaxf(row_max[hf], __shfl_xor_sync(0xffffffffu, row_max[hf], 1));
-      row_max[hf] = fmaxf(row_max[hf], __shfl_xor_sync(0xffffffffu, row_max[hf], 2));
-      const float m_new = fmaxf(m[hf], row_max[hf]);
-      corr[hf] = m_new == -INFINITY ? 1.f : expf(m[hf] - m_new);
-      float sum = 0.f;
+    for (int mt = 0; mt < LP_MT; ++mt)
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float v = m_new == -INFINITY ? 0.f : expf(p[nt][2 * hf + e] - m_new);
-          p[nt][2 * hf + e] = v;
-          sum += v;
-        }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      l[hf] = l[hf] * corr[hf] + sum;
-      m[hf] = m_new;
+        for (int e = 0; e < 4; ++e) sp[mt][nt][e] = 0.f;
+    for (int ks = warp; ks < k_steps; ks += 4) {
+      uint32_t b[2][2];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        b[nt][0] = *reinterpret_cast<const uint32_t*>(K + (nt * 8 + g) * LD + ks * 16 + 2 * t);
+        b[nt][1] = *reinterpret_cast<const uint32_t*>(K + (nt * 8 + g) * LD + ks * 16 + 2 * t + 8);
+      }
+#pragma unroll
+      for (int mt = 0; mt < LP_MT; ++mt) {
+        const bf16* Q = Qs + (16 * mt) * LD + ks * 16 + 2 * t;
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(Q + g * LD);
+        a[1] = *reinterpret_cast<const uint32_t*>(Q + (g + 8) * LD);
+        a[2] = *reinterpret_cast<const uint32_t*>(Q + g * LD + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(Q + (g + 8) * LD + 8);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) mma_bf16_16816(sp[mt][nt], a, b[nt][0], b[nt][1]);
+      }
     }
-    uint32_t pf[4];
-    pf[0] = pack_bf16(p[0][0], p[0][1]);
-    pf[1] = pack_bf16(p[0][2], p[0][3]);
-    pf[2] = pack_bf16(p[1][0], p[1][1]);
-    pf[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+    for (int mt = 0; mt < LP_MT; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          Sp[(warp * LP_ROWS + 16 * mt + g + 8 * (e >> 1)) * 17 + nt * 8 + 2 * t + (e & 1)] = sp[mt][nt][e];
+    __syncthreads();
+    // Every warp adds the four partial scores of its fragment positions and keeps the same softmax.
+    uint32_t pf[LP_MT][4];
+    float corr[LP_MT][2];
+#pragma unroll
+    for (int mt = 0; mt < LP_MT; ++mt) {
+      float p[2][4];
+      float row_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int hf = e >> 1, col = nt * 8 + 2 * t + (e & 1), j = j0 + col;
+          float sv = 0.f;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) sv += Sp[(w * LP_ROWS + 16 * mt + g + 8 * hf) * 17 + col];
+          const int pr = pos_r[mt][hf];
+          const bool seen = pr >= 0 && j <= pr && (window <= 0 || j > pr - window);
+          sv = seen ? sv * scale : -INFINITY;
+          p[nt][e] = sv;
+          row_max[hf] = fmaxf(row_max[hf], sv);
+        }
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        row_max[hf] = fmaxf(row_max[hf], __shfl_xor_sync(0xffffffffu, row_max[hf], 1));
+        row_max[hf] = fmaxf(row_max[hf], __shfl_xor_sync(0xffffffffu, row_max[hf], 2));
+        const float m_new = fmaxf(m[mt][hf], row_max[hf]);
+        corr[mt][hf] = m_new == -INFINITY ? 1.f : expf(m[mt][hf] - m_new);
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float v = m_new == -INFINITY ? 0.f : expf(p[nt][2 * hf + e] - m_new);
+            p[nt][2 * hf + e] = v;
+            sum += v;
+          }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l[mt][hf] = l[mt][hf] * corr[mt][hf] + sum;
+        m[mt][hf] = m_new;
+      }
+      pf[mt][0] = pack_bf16(p[0][0], p[0][1]);
+      pf[mt][1] = pack_bf16(p[0][2], p[0][3]);
+      pf[mt][2] = pack_bf16(p[1][0], p[1][1]);
+      pf[mt][3] = pack_bf16(p[1][2], p[1][3]);
+    }
     const int jm = lane >> 3;
 #pragma unroll
     for (int nc = 0; nc < NTV / 2; ++nc) {
@@ -654,29 +686,34 @@ latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, long long qa_tok
       uint32_t b[4];
       ldmatrix_x4_trans(b, K + ((jm & 1) * 8 + (lane & 7)) * LD + cw0 + (2 * nc + (jm >> 1)) * 8);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        acc[2 * nc][e] *= corr[e >> 1];
-        acc[2 * nc + 1][e] *= corr[e >> 1];
+      for (int mt = 0; mt < LP_MT; ++mt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[mt][2 * nc][e] *= corr[mt][e >> 1];
+          acc[mt][2 * nc + 1][e] *= corr[mt][e >> 1];
+        }
+        mma_bf16_16816(acc[mt][2 * nc], pf[mt], b[0], b[1]);
+        mma_bf16_16816(acc[mt][2 * nc + 1], pf[mt], b[2], b[3]);
       }
-      mma_bf16_16816(acc[2 * nc], pf, b[0], b[1]);
-      mma_bf16_16816(acc[2 * nc + 1], pf, b[2], b[3]);
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int hf = 0; hf < 2; ++hf) {
-    if (pos_r[hf] < 0) continue;
-    const int r = g + 8 * hf, tok = t0 + r / HG, h = h0 + r % HG;
-    const float gt = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)tok * gate_stride + h])));
-    const float f = gt / l[hf];
-    bf16* o = out + (size_t)tok * out_token + (size_t)h * out_head + cw0;
+  for (int mt = 0; mt < LP_MT; ++mt)
 #pragma unroll
-    for (int nt = 0; nt < NTV; ++nt) {
-      if (nt >= ntv) break;
-      *reinterpret_cast<__nv_bfloat162*>(o + nt * 8 + 2 * t) =
-          __floats2bfloat162_rn(acc[nt][2 * hf] * f, acc[nt][2 * hf + 1] * f);
+    for (int hf = 0; hf < 2; ++hf) {
+      if (pos_r[mt][hf] < 0) continue;
+      const int r = 16 * mt + g + 8 * hf, tok = t0 + r / HG, h = h0 + r % HG;
+      const float gt = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)tok * gate_stride + h])));
+      const float f = gt / l[mt][hf];
+      bf16* o = out + (size_t)tok * out_token + (size_t)h * out_head + cw0;
+#pragma unroll
+      for (int nt = 0; nt < NTV; ++nt) {
+        if (nt >= ntv) break;
+        *reinterpret_cast<__nv_bfloat162*>(o + nt * 8 + 2 * t) =
+            __floats2bfloat162_rn(acc[mt][nt][2 * hf] * f, acc[mt][nt][2 * hf + 1] * f);
+      }
     }
-  }
 }
 
 template <int HG, int NTV>
@@ -702,7 +739,7 @@ static int launch_latent_prefill(dim3 grid, size_t smem, cudaStream_t stream, co
 }
 
 // Tokens per tile of the prompt kernel for a number of heads (the tile list is made for it on the host).
-LLMRS_API int llmrs_latent_prefill_tile_tokens(int n_heads) { return n_heads >= 4 ? 4 : 16; }
+LLMRS_API int llmrs_latent_prefill_tile_tokens(int n_heads) { return n_heads >= 4 ? LP_ROWS / 4 : LP_ROWS; }
 
 // bfloat16 only. tiles: int32 [n_tiles][2] = first token of the step, tokens (at most the tile size, one request's,
 // consecutive positions). Returns -2 (and launches nothing) when the sizes do not fit this kernel.
@@ -720,7 +757,7 @@ LLMRS_API int llmrs_latent_attention_prefill(const void* qa, long long qa_token,
   if (n_tiles == 0) return 0;
   const int hg = n_heads >= 4 ? 4 : 1;
   const int LD = rank + dr + 8;
-  const size_t smem = (size_t)3 * 16 * LD * sizeof(__nv_bfloat16) + (size_t)4 * 16 * 17 * sizeof(float);
+  const size_t smem = (size_t)(LP_ROWS + 2 * 16) * LD * sizeof(__nv_bfloat16) + (size_t)4 * LP_ROWS * 17 * sizeof(float);
   dim3 grid(n_tiles, (n_heads + hg - 1) / hg);
   LLMRS_REQUIRE(grid.y <= 65535, "latent_attention_prefill: too many heads");
 #define LLMRS_LP_ARGS                                                                                               \

@@ -908,7 +908,7 @@ def latent_attention(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cach
 
 def latent_prefill_tile_tokens(n_heads: int) -> int:
     """Tokens per tile of ``latent_attention_prefill`` for a number of heads."""
-    return 4 if n_heads >= 4 else 16
+    return int(_lib().llmrs_latent_prefill_tile_tokens(n_heads))
 
 
 def latent_attention_prefill(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cache: torch.Tensor, table, ctx,

@@ -80,6 +80,7 @@ class LatentAttention(Mixer):
         if set(self.names) != set(self.ROLES):
             raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
         self.q_width = n_heads * (dim + rot_dim)
+        self._tile = None
 
     def _name(self, role: str) -> str:
         return self.prefix + self.names[role]
@@ -121,15 +122,20 @@ class LatentAttention(Mixer):
                          planes=(self.rank, self.rot_dim))
 
     # -- the step's plan: tiles of a prompt's tokens for the tensor-core kernel -------------------------------------
+    def _tile_tokens(self) -> int:
+        if self._tile is None:      # asked of the kernel library at first use: constructing a part needs no library
+            self._tile = ops.latent_prefill_tile_tokens(self.n_heads)
+        return self._tile
+
     def plan_key(self):
-        return ("latent_attention_tiles", ops.latent_prefill_tile_tokens(self.n_heads))
+        return ("latent_attention_tiles", self._tile_tokens())
 
     def plan(self, step: StepInfo) -> Plan:
         """Steps that bring a prompt's portion are cut into tiles of tokens (none for steps of single tokens, which
         the CUDA-core kernel takes with its keys cut over blocks, and which may be replayed from a graph)."""
         if step.for_graph or step.n_tokens < PREFILL_MIN_TOKENS or int(np.max(step.n_new, initial=0)) <= 1:
             return Plan(arrays={"tiles": np.zeros((0, 2), np.int32)}, values={"n_tiles": 0})
-        tiles = portion_tiles(step.q_start, step.n_new, ops.latent_prefill_tile_tokens(self.n_heads))
+        tiles = portion_tiles(step.q_start, step.n_new, self._tile_tokens())
         return Plan(arrays={"tiles": tiles}, values={"n_tiles": int(tiles.shape[0])})
 
     def _tiles(self, ctx):
@@ -141,7 +147,7 @@ class LatentAttention(Mixer):
         n_new = ctx.n_new.cpu().numpy()
         if ctx.n_tokens < PREFILL_MIN_TOKENS or int(n_new.max(initial=0)) <= 1:
             return None
-        tiles = portion_tiles(ctx.q_start.cpu().numpy(), n_new, ops.latent_prefill_tile_tokens(self.n_heads))
+        tiles = portion_tiles(ctx.q_start.cpu().numpy(), n_new, self._tile_tokens())
         return torch.from_numpy(tiles).to(ctx.n_new.device), int(tiles.shape[0])
 
     def forward(self, x, ctx, cache):
