@@ -113,7 +113,8 @@ delta_rule_kernel(const float* __restrict__ prep, float* __restrict__ state, con
       cp_async_wait<0>();
     }
     __syncthreads();
-    for (int tt = 0; tt < cn; ++tt) {
+#pragma unroll 4
+    for (int tt = 0; tt < cn; ++tt) {      // unrolled: the next tokens' rows are fetched under this token's shuffles
       const float vj = s_v[buf][tt][tid / DR_LANES];
       float us[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
