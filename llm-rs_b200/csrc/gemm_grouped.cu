@@ -215,29 +215,31 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_grouped_mma_kernel(const Grou
       cp_async_wait<0>();
     }
     __syncthreads();
+    // Fragments come by ldmatrix: lane l gives the address of row l % 8 of 8 x 8 piece l / 8.
+    const int lm = lane >> 3, lr = lane & 7;
 #pragma unroll
     for (int kk = 0; kk < GM_BK; kk += 16) {
       uint32_t af[2][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int r = wm + 16 * i + g;
-        af[i][0] = *reinterpret_cast<const uint32_t*>(&As[stage][r][kk + 2 * t]);
-        af[i][1] = *reinterpret_cast<const uint32_t*>(&As[stage][r + 8][kk + 2 * t]);
-        af[i][2] = *reinterpret_cast<const uint32_t*>(&As[stage][r][kk + 2 * t + 8]);
-        af[i][3] = *reinterpret_cast<const uint32_t*>(&As[stage][r + 8][kk + 2 * t + 8]);
-      }
+      for (int i = 0; i < 2; ++i)      // pieces: rows 0-7 / 8-15 at k 0-7, then the same at k 8-15
+        ldmatrix_x4(af[i], &As[stage][wm + 16 * i + (lm & 1) * 8 + lr][kk + (lm >> 1) * 8]);
 #pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        const int n = wn + 8 * j + g;
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Bs[stage][n][kk + 2 * t]);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Bs[stage][n][kk + 2 * t + 8]);
+      for (int j = 0; j < NT; j += 2) {
+        uint32_t b[4];                 // pieces: columns j at k 0-7 / 8-15, then columns j + 1
+        ldmatrix_x4(b, &Bs[stage][wn + 8 * (j + (lm >> 1)) + lr][kk + (lm & 1) * 8]);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) mma_bf16_16816(acc[i][j], af[i], b0, b1);
+        for (int i = 0; i < 2; ++i) {
+          mma_bf16_16816(acc[i][j], af[i], b[0], b[1]);
+          mma_bf16_16816(acc[i][j + 1], af[i], b[2], b[3]);
+        }
         if (GLU) {
-          const uint32_t c0 = *reinterpret_cast<const uint32_t*>(&B2s[stage][n][kk + 2 * t]);
-          const uint32_t c1 = *reinterpret_cast<const uint32_t*>(&B2s[stage][n][kk + 2 * t + 8]);
+          uint32_t c[4];
+          ldmatrix_x4(c, &B2s[stage][wn + 8 * (j + (lm >> 1)) + lr][kk + (lm & 1) * 8]);
 #pragma unroll
-          for (int i = 0; i < 2; ++i) mma_bf16_16816(acc2[i][j], af[i], c0, c1);
+          for (int i = 0; i < 2; ++i) {
+            mma_bf16_16816(acc2[i][j], af[i], c[0], c[1]);
+            mma_bf16_16816(acc2[i][j + 1], af[i], c[2], c[3]);
+          }
         }
       }
     }
