@@ -31,6 +31,7 @@ struct GroupedGemmArgs {
   const int* n_tiles;       // grouped mode: number of tiles on the device
   const int* src;           // grouped mode: sorted row -> row of X (null: the row itself)
   int round_x;
+  int tile_rows;            // grouped mode: the most rows a tile of the list has (64 or 128)
   float limit, alpha, shift;
 };
 
@@ -52,9 +53,12 @@ __global__ void __launch_bounds__(GG_THREADS) gemm_grouped_kernel(const GroupedG
 
   const int tid = threadIdx.x;
   int group, m0, rows;
-  if (a.tiles != nullptr) {
-    if ((int)blockIdx.y >= *a.n_tiles) return;
-    group = a.tiles[3 * blockIdx.y], m0 = a.tiles[3 * blockIdx.y + 1], rows = a.tiles[3 * blockIdx.y + 2];
+  if (a.tiles != nullptr) {      // a tile of the list may hold more rows than this kernel's: several blocks share it
+    const int pieces = a.tile_rows / GG_BM, tile = blockIdx.y / pieces, piece = blockIdx.y % pieces;
+    if (tile >= *a.n_tiles) return;
+    group = a.tiles[3 * tile], m0 = a.tiles[3 * tile + 1] + GG_BM * piece;
+    rows = min(GG_BM, a.tiles[3 * tile + 2] - GG_BM * piece);
+    if (rows <= 0) return;
   } else {
     group = blockIdx.z, m0 = blockIdx.y * GG_BM, rows = min(GG_BM, a.M - m0);
   }
@@ -136,17 +140,18 @@ __global__ void __launch_bounds__(GG_THREADS) gemm_grouped_kernel(const GroupedG
 
 // ---------------------------------------------------------------------------------
 // The same products on the tensor cores for bfloat16 operands (mma.sync m16n8k16, float32 accumulators): tiles of
-// 64 rows x 128 columns (64 of each product for the gated unit), k in steps of 32 through a double buffer of 16-byte asynchronous copies. Eight warps as
-// 2 x 4, each 32 rows x 32 (or 2 x 16) columns. Shared rows are 40 elements apart, which
+// 64 or 128 rows x 128 columns (64 of each product for the gated unit), k in steps of 32 through a double buffer of 16-byte asynchronous copies. Eight warps as
+// 2 x 4, each 32 or 64 rows x 32 (or 2 x 16) columns. Shared rows are 40 elements apart, which
 // spreads the fragments' 32-bit reads over all banks. A row's sums run over k in the same order whichever rows
 // share its tile. Needs K % 8 == 0 and 16-byte aligned rows of X and W.
 // ---------------------------------------------------------------------------------
-constexpr int GM_BM = 64, GM_BK = 32, GM_LD = GM_BK + 8, GM_THREADS = 256;
+constexpr int GM_BK = 32, GM_LD = GM_BK + 8, GM_THREADS = 256;
 // Columns of a tile: 128, or 64 of each of the two products of the gated unit (the same shared memory either way).
 template <bool GLU> struct GmCols { static constexpr int value = GLU ? 64 : 128; };
 
-template <typename TO, bool GLU>
+template <typename TO, bool GLU, int MT>      // MT: 16-row pieces per warp; the tile has 32 * MT rows
 __global__ void __launch_bounds__(GM_THREADS) gemm_grouped_mma_kernel(const GroupedGemmArgs a) {
+  constexpr int GM_BM = 32 * MT;
   constexpr int GM_BN = GmCols<GLU>::value, NT = GM_BN / 32;      // NT: 8-column pieces per warp
   __shared__ __align__(16) __nv_bfloat16 As[2][GM_BM][GM_LD];
   __shared__ __align__(16) __nv_bfloat16 Bs[2][GM_BN][GM_LD];
@@ -175,13 +180,18 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_grouped_mma_kernel(const Grou
   const __nv_bfloat16* w2 = GLU ? (const __nv_bfloat16*)a.w2 + (size_t)group * a.w_batch : nullptr;
   const int n0 = blockIdx.x * GM_BN;
 
-  // Copies of one k step: A 64 rows x 4 pieces of 8 elements (one per thread), B 128 x 4 (two per thread).
+  // Copies of one k step: rows x 4 pieces of 8 elements; a thread takes rows tid / 4, tid / 4 + 64, ...
   const int a_row = tid >> 2, piece = (tid & 3) * 8;
-  const long long a_off = row_off[a_row];
+  long long a_off[GM_BM / 64];
+#pragma unroll
+  for (int h = 0; h < GM_BM / 64; ++h) a_off[h] = row_off[a_row + 64 * h];
   auto issue = [&](int stage, int k0) {
     const int k = k0 + piece;
     const int kb = k < a.K ? min(16, (a.K - k) * 2) : 0;      // bytes of this piece inside K (K % 8 == 0: 0 or 16)
-    cp_async_16(&As[stage][a_row][piece], x + (a_off >= 0 ? a_off : 0) + (kb ? k : 0), a_off >= 0 ? kb : 0);
+#pragma unroll
+    for (int h = 0; h < GM_BM / 64; ++h)
+      cp_async_16(&As[stage][a_row + 64 * h][piece], x + (a_off[h] >= 0 ? a_off[h] : 0) + (kb ? k : 0),
+                  a_off[h] >= 0 ? kb : 0);
 #pragma unroll
     for (int h = 0; h < GM_BN / 64; ++h) {
       const int r = a_row + 64 * h, n = n0 + r;
@@ -192,11 +202,11 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_grouped_mma_kernel(const Grou
     cp_async_commit();
   };
 
-  const int wm = (warp >> 2) * 32, wn = (warp & 3) * (8 * NT);
+  const int wm = (warp >> 2) * (16 * MT), wn = (warp & 3) * (8 * NT);
   const int g = lane >> 2, t = lane & 3;
-  float acc[2][NT][4], acc2[GLU ? 2 : 1][GLU ? NT : 1][4];
+  float acc[MT][NT][4], acc2[GLU ? MT : 1][GLU ? NT : 1][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MT; ++i)
 #pragma unroll
     for (int j = 0; j < NT; ++j)
 #pragma unroll
@@ -219,16 +229,16 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_grouped_mma_kernel(const Grou
     const int lm = lane >> 3, lr = lane & 7;
 #pragma unroll
     for (int kk = 0; kk < GM_BK; kk += 16) {
-      uint32_t af[2][4];
+      uint32_t af[MT][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i)      // pieces: rows 0-7 / 8-15 at k 0-7, then the same at k 8-15
+      for (int i = 0; i < MT; ++i)     // pieces: rows 0-7 / 8-15 at k 0-7, then the same at k 8-15
         ldmatrix_x4(af[i], &As[stage][wm + 16 * i + (lm & 1) * 8 + lr][kk + (lm >> 1) * 8]);
 #pragma unroll
       for (int j = 0; j < NT; j += 2) {
         uint32_t b[4];                 // pieces: columns j at k 0-7 / 8-15, then columns j + 1
         ldmatrix_x4(b, &Bs[stage][wn + 8 * (j + (lm >> 1)) + lr][kk + (lm & 1) * 8]);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < MT; ++i) {
           mma_bf16_16816(acc[i][j], af[i], b[0], b[1]);
           mma_bf16_16816(acc[i][j + 1], af[i], b[2], b[3]);
         }
@@ -236,7 +246,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_grouped_mma_kernel(const Grou
           uint32_t c[4];
           ldmatrix_x4(c, &B2s[stage][wn + 8 * (j + (lm >> 1)) + lr][kk + (lm & 1) * 8]);
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
+          for (int i = 0; i < MT; ++i) {
             mma_bf16_16816(acc2[i][j], af[i], c[0], c[1]);
             mma_bf16_16816(acc2[i][j + 1], af[i], c[2], c[3]);
           }
@@ -247,7 +257,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_grouped_mma_kernel(const Grou
   }
   TO* out = (TO*)a.out + (a.tiles ? 0 : (size_t)group * a.out_batch);
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MT; ++i)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int r = wm + 16 * i + g + 8 * half;
@@ -270,12 +280,12 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_grouped_mma_kernel(const Grou
     }
 }
 
-template <typename TO>
+template <typename TO, int MT>
 static int launch_grouped_mma(const GroupedGemmArgs& a, dim3 grid, cudaStream_t stream) {
   if (a.w2 != nullptr)
-    gemm_grouped_mma_kernel<TO, true><<<grid, GM_THREADS, 0, stream>>>(a);
+    gemm_grouped_mma_kernel<TO, true, MT><<<grid, GM_THREADS, 0, stream>>>(a);
   else
-    gemm_grouped_mma_kernel<TO, false><<<grid, GM_THREADS, 0, stream>>>(a);
+    gemm_grouped_mma_kernel<TO, false, MT><<<grid, GM_THREADS, 0, stream>>>(a);
   return llmrs_launch_status("gemm_grouped (tensor cores)");
 }
 
@@ -298,27 +308,33 @@ static int launch_grouped(const GroupedGemmArgs& a, dim3 grid, cudaStream_t stre
 LLMRS_API int llmrs_gemm_grouped(const void* x, int x_dtype, long long x_stride, long long x_batch, const void* w,
                                  const void* w2, int w_dtype, long long w_batch, void* out, int out_dtype,
                                  long long out_stride, long long out_batch, int M, int N, int K, int batches,
-                                 const int* tiles, const int* n_tiles, int max_tiles, const int* src, int round_x,
-                                 float limit, float alpha, float shift, cudaStream_t stream) {
+                                 const int* tiles, const int* n_tiles, int max_tiles, int tile_rows, const int* src,
+                                 int round_x, float limit, float alpha, float shift, cudaStream_t stream) {
   LLMRS_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_grouped: bad sizes M=%d N=%d K=%d", M, N, K);
   LLMRS_REQUIRE((tiles != nullptr) != (batches > 0), "gemm_grouped: either a tile list or a number of batches");
   LLMRS_REQUIRE(tiles == nullptr || n_tiles != nullptr, "gemm_grouped: a tile list needs its length");
+  LLMRS_REQUIRE(tiles == nullptr || tile_rows == 64 || tile_rows == 128, "gemm_grouped: tiles of 64 or 128 rows");
+  if (tiles == nullptr) tile_rows = M >= 128 ? 128 : 64;      // batched mode: the rows are cut here
   if (M == 0) return 0;
   GroupedGemmArgs a;
   a.x = x, a.x_stride = x_stride, a.x_batch = x_batch, a.w = w, a.w2 = w2, a.w_batch = w_batch;
   a.out = out, a.out_stride = out_stride, a.out_batch = out_batch, a.M = M, a.N = N, a.K = K;
-  a.tiles = tiles, a.n_tiles = n_tiles, a.src = src, a.round_x = round_x;
+  a.tiles = tiles, a.n_tiles = n_tiles, a.src = src, a.round_x = round_x, a.tile_rows = tile_rows;
   a.limit = limit, a.alpha = alpha, a.shift = shift;
-  dim3 grid((N + GG_BN - 1) / GG_BN, tiles ? max_tiles : (M + GG_BM - 1) / GG_BM, tiles ? 1 : batches);
+  dim3 grid((N + GG_BN - 1) / GG_BN, tiles ? max_tiles * (tile_rows / GG_BM) : (M + GG_BM - 1) / GG_BM,
+            tiles ? 1 : batches);
   LLMRS_REQUIRE(grid.y >= 1 && grid.y <= 65535 && grid.z <= 65535, "gemm_grouped: too many tiles or batches");
   // bfloat16 operands whose rows can be copied 16 bytes at a time go to the tensor cores.
   if (g_grouped_mma && x_dtype == LLMRS_BF16 && w_dtype == LLMRS_BF16 && K % 8 == 0 && x_stride % 8 == 0 &&
       x_batch % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && (!w2 || ((uintptr_t)w2 & 15) == 0) &&
       (N * (long long)K) % 8 == 0) {
     const int cols = w2 ? GmCols<true>::value : GmCols<false>::value;
-    dim3 mgrid((N + cols - 1) / cols, grid.y, grid.z);
-    return out_dtype == LLMRS_BF16 ? launch_grouped_mma<__nv_bfloat16>(a, mgrid, stream)
-                                   : launch_grouped_mma<float>(a, mgrid, stream);
+    dim3 mgrid((N + cols - 1) / cols, tiles ? max_tiles : (M + tile_rows - 1) / tile_rows, grid.z);
+    if (tile_rows == 128)
+      return out_dtype == LLMRS_BF16 ? launch_grouped_mma<__nv_bfloat16, 4>(a, mgrid, stream)
+                                     : launch_grouped_mma<float, 4>(a, mgrid, stream);
+    return out_dtype == LLMRS_BF16 ? launch_grouped_mma<__nv_bfloat16, 2>(a, mgrid, stream)
+                                   : launch_grouped_mma<float, 2>(a, mgrid, stream);
   }
   const int key = x_dtype * 4 + w_dtype * 2 + out_dtype;
   switch (key) {

@@ -715,7 +715,14 @@ def tanh_slice(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
 
 
 # -- many small products in one launch ----------------------------------------------------------------
-GROUPED_TILE_ROWS = 64
+GROUPED_TILE_ROWS = 64      # rows of a tile of the grouped product; 128 where groups have many rows (``grouped_tile_rows``)
+
+
+def grouped_tile_rows(n_rows: int, n_groups: int) -> int:
+    """Rows per tile for ``moe_sort`` and ``gemm_grouped``: 128 when the groups hold some hundred rows each (prompts:
+    a larger tile reads the weights half as often), else 64."""
+    return 128 if n_rows >= 96 * n_groups else GROUPED_TILE_ROWS
+
 
 
 def _strides3(t: torch.Tensor, name: str):
@@ -748,16 +755,17 @@ def gemm_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, round_x: b
     N = w.size(1)
     _check(_lib().llmrs_gemm_grouped(
         _ptr(x), dtype_code(x.dtype), _LL(xs), _LL(xb), _ptr(w), None, dtype_code(w.dtype), _LL(N * K), _ptr(out),
-        dtype_code(out.dtype), _LL(os_), _LL(ob), M, N, K, B, None, None, 0, None, int(round_x), ctypes.c_float(0),
+        dtype_code(out.dtype), _LL(os_), _LL(ob), M, N, K, B, None, None, 0, 0, None, int(round_x), ctypes.c_float(0),
         ctypes.c_float(0), ctypes.c_float(0), _stream()), "gemm_batched")
     return out
 
 
 def gemm_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor,
                  src: Optional[torch.Tensor], w2: Optional[torch.Tensor] = None, round_x: bool = False,
-                 limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0) -> torch.Tensor:
+                 limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0,
+                 tile_rows: int = GROUPED_TILE_ROWS) -> torch.Tensor:
     """Rows sorted by group against each group's own weights: ``out[r] = w[g(r)] @ x[src[r]]`` for the rows of every
-    tile (``tiles`` [max, 3] = group, first row, rows; ``n_tiles`` on the device; from ``moe_sort``). With ``w2`` the
+    tile (``tiles`` [max, 3] = group, first row, at most ``tile_rows`` rows; ``n_tiles`` on the device; from ``moe_sort``). With ``w2`` the
     gated unit ``g * sigmoid(alpha * g) * (u + shift)``, g = min(w x, limit), u = clamp(w2 x, -limit, limit)."""
     _need(x, "x", contiguous=False)
     _need(w, "w")
@@ -772,7 +780,7 @@ def gemm_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tiles: tor
     _check(_lib().llmrs_gemm_grouped(
         _ptr(x), dtype_code(x.dtype), _LL(_row_stride(x, "x")), _LL(0), _ptr(w), _ptr(w2), dtype_code(w.dtype),
         _LL(N * K), _ptr(out), dtype_code(out.dtype), _LL(out.stride(0)), _LL(0), out.size(0), N, K, 0, _ptr(tiles),
-        _ptr(n_tiles), tiles.size(0), _ptr(src), int(round_x), ctypes.c_float(limit), ctypes.c_float(alpha),
+        _ptr(n_tiles), tiles.size(0), tile_rows, _ptr(src), int(round_x), ctypes.c_float(limit), ctypes.c_float(alpha),
         ctypes.c_float(shift), _stream()), "gemm_grouped")
     return out
 
@@ -792,7 +800,7 @@ def moe_route_table(token_ids: torch.Tensor, table: torch.Tensor, n_experts: int
     return expert_of, weight_of
 
 
-def moe_sort(expert_of: torch.Tensor, top: int, n_experts: int):
+def moe_sort(expert_of: torch.Tensor, top: int, n_experts: int, tile_rows: int = GROUPED_TILE_ROWS):
     """Order the assignments by expert. Returns (row_of [assignments], src_token [assignments], tiles [max, 3],
     n_tiles [1]): see ``gemm_grouped``."""
     _need(expert_of, "expert_of", torch.int32)
@@ -800,11 +808,11 @@ def moe_sort(expert_of: torch.Tensor, top: int, n_experts: int):
     dev = expert_of.device
     row_of = torch.empty((n,), dtype=torch.int32, device=dev)
     src_token = torch.empty((n,), dtype=torch.int32, device=dev)
-    max_tiles = -(-n // GROUPED_TILE_ROWS) + n_experts
+    max_tiles = -(-n // tile_rows) + n_experts
     tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=dev)
     n_tiles = torch.empty((1,), dtype=torch.int32, device=dev)
     _check(_lib().llmrs_moe_sort(_ptr(expert_of), _ptr(row_of), _ptr(src_token), _ptr(tiles), _ptr(n_tiles), n, top,
-                                 n_experts, GROUPED_TILE_ROWS, _stream()), "moe_sort")
+                                 n_experts, tile_rows, _stream()), "moe_sort")
     return row_of, src_token, tiles, n_tiles
 
 

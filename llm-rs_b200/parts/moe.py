@@ -75,13 +75,14 @@ class MixtureOfExperts(FeedForward):
     def forward(self, x, ctx):
         """x: the step's rows, float32 (the residual stream) or the activation type. Returns float32 [tokens, hidden]."""
         expert_of, weight_of = ops.moe_route_table(ctx.token_ids, self.table, self.n_experts)
-        row_of, src_token, tiles, n_tiles = ops.moe_sort(expert_of, self.top, self.n_experts)
         n_rows = expert_of.numel()
+        tile_rows = ops.grouped_tile_rows(n_rows, self.n_experts)
+        row_of, src_token, tiles, n_tiles = ops.moe_sort(expert_of, self.top, self.n_experts, tile_rows)
         if self.act_dtype == torch.bfloat16 and x.dtype == torch.float32:
             x = ops.token_shift(x, None, None, None, torch.bfloat16)     # the rows as activations: the tensor cores' type
         act = torch.empty((n_rows, self.expert_size), dtype=self.act_dtype, device=x.device)
         ops.gemm_grouped(x, self.w_gate, act, tiles, n_tiles, src_token, w2=self.w_up, limit=self.limit,
-                         alpha=self.alpha, shift=self.up_shift)
+                         alpha=self.alpha, shift=self.up_shift, tile_rows=tile_rows)
         rows = torch.empty((n_rows, self.hidden_size), dtype=torch.float32, device=x.device)
-        ops.gemm_grouped(act, self.w_down, rows, tiles, n_tiles, None)
+        ops.gemm_grouped(act, self.w_down, rows, tiles, n_tiles, None, tile_rows=tile_rows)
         return ops.moe_combine(rows, row_of, weight_of, self.top)

@@ -164,10 +164,11 @@ def test_batched_product_over_heads(M, B, N, K, pad, tensor_cores):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,n_tokens", [(4, 2, 50), (3, 3, 7), (1, 1, 5), (37, 4, 300), (8, 1, 1)])
+@pytest.mark.parametrize("experts,top,n_tokens", [(4, 2, 50), (3, 3, 7), (1, 1, 5), (37, 4, 300), (8, 1, 1), (2, 1, 400), (4, 2, 300)])
 def test_mixture_of_experts_against_plain(dtype, experts, top, n_tokens):
     """Routing by the table, the sort by expert, both grouped products and the weighted sum; token ids repeat, some
-    experts get no token, tiles of rows are cut inside an expert's run (300 tokens x 4 over 37 experts)."""
+    experts get no token, tiles of rows are cut inside an expert's run (300 tokens x 4 over 37 experts); with some hundred
+    rows an expert the tiles have 128 rows instead of 64 (the last two cases)."""
     from llm_rs_b200 import ops
     from llm_rs_b200.parts import Runtime
     from llm_rs_b200.parts.moe import MixtureOfExperts
