@@ -19,6 +19,8 @@ A "step" is one decode step of the whole batch. The default is batch 8 at a cont
 
 The K timed steps run back to back as five runs of K/5 steps with a CUDA event between them: ``value`` and
 ``ms_per_step`` are the median run's, ``repeats`` gives the runs' spread and the mean over all K steps.
+``--workload rusadra`` measures the Rusadra design beside Qwen3 at equal size instead (see DESIGN_SIZES below); the
+default workload and its JSON line are unchanged by it.
 Fractions are given against two denominators: the peaks measured on this pool (MEASURED_PEAKS.json beside
 this file when present, else 6.65 TB/s and 1.59 PFLOP/s) and the nominal figures of the part (7.7 TB/s,
 2.25 PFLOP/s dense bf16). Only N = 1 is supported: the engine is a single-GPU engine.
@@ -373,7 +375,9 @@ def main():
                     "with bytes, flops and the fraction of the peaks to standard error, the rows as JSON to standard output")
     ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS, "rusadra"],
                     help="decode: the benchmark contract (default). mixed14b / stress32b: a whole serving run "
-                    "through the engine on the layer sizes of Qwen3-14B / Qwen3-32B")
+                    "through the engine on the layer sizes of Qwen3-14B / Qwen3-32B. rusadra: prefill and decode of the "
+                    "Rusadra design beside Qwen3 at equal width, depth, vocabulary and active feed-forward width, with "
+                    "every kernel class's fraction of the device's peaks")
     ap.add_argument("--pool-tokens", type=int, default=0, help="size of the cache pool of a --workload run in "
                     "tokens (default: what holds every request whole); smaller makes the scheduler preempt")
     args = ap.parse_args()
