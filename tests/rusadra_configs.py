@@ -77,9 +77,19 @@ RUSADRA_E = {
         (_latent(4, 8, 8, 24, 32, 1, base=50.0), None),
         (_latent(6, 16, 16, 16, 64, 64, base=1e5, kv_from=0), None))}
 
+# Two attention layers that own rows of the same shape and window (one page group with two entries, one block table
+# for both), a reader of the SECOND, a recurrent layer between them; pages of 32 keys.
+RUSADRA_F = {
+    "architecture": "Rusadra", "vocab": 150, "width": 64, "norm": {"eps": 1e-6}, "logit_softcap": 20.0,
+    "layers": _layers(
+        (_latent(4, 16, 16, 16, 64, 24, base=1e4), _moe(32, 1.0, 4, 2)),
+        (_delta(2, 32, 8), None),
+        (_latent(2, 32, 16, 32, 64, 24, base=1e4), _moe(32, 1.0, 4, 1)),
+        (_latent(4, 16, 16, 16, 64, 24, base=1e4, kv_from=2), None))}
+
 # name -> (config.json, seed, sigma of matrices, page size)
 RUSADRA = {"A": (RUSADRA_A, 3, 0.08, 16), "B": (RUSADRA_B, 4, 0.1, 8), "C": (RUSADRA_C, 5, 0.05, 16),
-           "D": (RUSADRA_D, 6, 0.1, 16), "E": (RUSADRA_E, 7, 0.1, 16)}
+           "D": (RUSADRA_D, 6, 0.1, 16), "E": (RUSADRA_E, 7, 0.1, 16), "F": (RUSADRA_F, 8, 0.1, 32)}
 
 
 def write_rusadra_model(name: str, folder: str, dtype=torch.bfloat16) -> str:

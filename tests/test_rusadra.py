@@ -86,6 +86,16 @@ def test_spec_run_order_shared_pages_and_names():
     assert spec_b.layers[0].mixer.params["cache_window"] == 1000 and spec_b.layers[1].mixer.params["window"] == 7
 
 
+def test_owners_of_equal_rows_share_a_page_group():
+    from llm_rs_b200.cache import plan_groups
+    from rusadra_configs import RUSADRA_F
+    spec = resolve_architecture(RUSADRA_F).build_spec(RusadraConfig.from_dict(RUSADRA_F))
+    needs = DecoderModel(spec).cache_needs()
+    groups, entry_group, entry_index = plan_groups(needs, spec.run_order, 8)
+    assert len(groups) == 1 and groups[0].entries == [0, 2]
+    assert entry_group == [0, None, 0, 0] and entry_index == [0, None, 1, 1]      # the reader sees the second owner's rows
+
+
 def test_random_folder_has_valid_tables_and_loads_by_name(tmp_path):
     from llm_rs_b200.weights import load_weights
     path = write_rusadra_model("A", str(tmp_path))
