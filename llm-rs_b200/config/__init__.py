@@ -4,6 +4,8 @@ from .registry import (ArchitectureEntry, architecture_names, load_config,
                        register_architecture, resolve_architecture, unregister_architecture)
 from .qwen3 import Qwen3Config
 from .rusadra import RusadraConfig
+from .pusazen import PusazenConfig
 
 __all__ = ["ConfigError", "ArchitectureEntry", "architecture_names", "load_config",
-           "register_architecture", "resolve_architecture", "unregister_architecture", "Qwen3Config", "RusadraConfig"]
+           "register_architecture", "resolve_architecture", "unregister_architecture", "Qwen3Config", "RusadraConfig",
+           "PusazenConfig"]

@@ -1,0 +1,680 @@
+// Attention over the paged cache with options on the score: a soft cap, a sink in the softmax's denominator, and a
+// choice of masks; keys and values may have different widths.
+//
+//   score  = (q . k) * scale;  with softcap > 0: score = softcap * tanh(score / softcap)
+//   mask   causal (key <= query), plus one of
+//            window  key > query - size
+//            chunk   floor(key / size) == floor(query / size), chunks counted from position 0 of the sequence
+//   weights  exp(score - m) / (sum over visible keys + exp(sink_h - m)); the sink (one learned number per query head)
+//            has no key and no value: it only takes weight away. Null: no sink.
+//
+// A page holds, per key/value head, page_size rows of dk (keys) and then page_size rows of dv (values).
+//
+//   prepare   RMS norm over the WHOLE q row (all heads at once) and the whole k row with weights of that size
+//             (null: no norm), rotation of the first rot_dims channels of every head (channel i with i + rot_dims/2,
+//             angle position * inv_freq[i], made in double), q rewritten in place, k and v written into their pages;
+//   prefill   16 queries of one request per block against the keys they may see, online softmax (any type);
+//             bfloat16 with dk, dv multiples of 16 up to 128: 64 queries per block on the tensor cores (mma.sync);
+//   decode    one query per request: the visible keys are cut into runs that separate blocks take (a warp per key,
+//             lanes over channels), and a second kernel merges the runs and adds the sink.
+// Scores, weights and sums are float32.
+#include "common.cuh"
+#include "mma_util.cuh"
+
+enum { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_CHUNK = 2 };
+
+struct ScoreOpts {
+  float scale, softcap;
+  const float* sink;
+  int mask, size;
+};
+
+__device__ __forceinline__ int first_visible(const ScoreOpts& o, int pos) {
+  if (o.mask == MASK_WINDOW) return max(0, pos - o.size + 1);
+  if (o.mask == MASK_CHUNK) return (pos / o.size) * o.size;
+  return 0;
+}
+__device__ __forceinline__ float capped(const ScoreOpts& o, float s) {
+  s *= o.scale;
+  return o.softcap > 0.f ? o.softcap * tanhf(s / o.softcap) : s;
+}
+__device__ __host__ __forceinline__ size_t page_head_offset(int page, int kvh, int n_kv_heads, int page_size, int dk,
+                                                            int dv) {
+  return ((size_t)page * n_kv_heads + kvh) * (size_t)page_size * (dk + dv);
+}
+
+// ---------------------------------------------------------------------------------
+// prepare
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void scored_prepare_kernel(T* __restrict__ q, long long q_stride, const T* __restrict__ k,
+                                      long long k_stride, const T* __restrict__ v, long long v_stride,
+                                      const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
+                                      const double* __restrict__ inv_freq, const int* __restrict__ positions,
+                                      const int* __restrict__ token_req, const int* __restrict__ block_table,
+                                      int table_stride, T* __restrict__ cache, int n_q_heads, int n_kv_heads, int dk,
+                                      int dv, int rot_dims, int page_size, float eps) {
+  extern __shared__ float sm[];
+  __shared__ float red[33];
+  const int t = blockIdx.x, pos = positions[t];
+  const int wq = n_q_heads * dk, wk = k ? n_kv_heads * dk : 0, half = rot_dims / 2;
+  float* xq = sm;              // [wq]
+  float* xk = xq + wq;         // [wk]
+  float* cs = xk + wk;         // [half][2]
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < wq; c += blockDim.x) {
+    const float f = to_float(q[(size_t)t * q_stride + c]);
+    xq[c] = f;
+    sq = fmaf(f, f, sq);
+  }
+  for (int c = threadIdx.x; c < wk; c += blockDim.x) {
+    const float f = to_float(k[(size_t)t * k_stride + c]);
+    xk[c] = f;
+    sk = fmaf(f, f, sk);
+  }
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double s, c;
+    sincos((double)pos * inv_freq[i], &s, &c);
+    cs[2 * i] = (float)c;
+    cs[2 * i + 1] = (float)s;
+  }
+  sq = block_sum(sq, red);
+  sk = block_sum(sk, red);
+  const float inv_q = q_norm_w ? 1.0f / sqrtf(sq / (float)wq + eps) : 1.0f;
+  const float inv_k = (k_norm_w && wk) ? 1.0f / sqrtf(sk / (float)wk + eps) : 1.0f;
+  auto turned = [&](const float* x, const float* w, float inv, int head, int i) {
+    const int c = head * dk + i;
+    float a = x[c] * inv * (w ? w[c] : 1.0f);
+    if (i < rot_dims) {
+      const int j = i < half ? i : i - half;
+      const int pc = head * dk + (i < half ? i + half : i - half);
+      const float b = x[pc] * inv * (w ? w[pc] : 1.0f);
+      a = i < half ? a * cs[2 * j] - b * cs[2 * j + 1] : a * cs[2 * j] + b * cs[2 * j + 1];
+    }
+    return a;
+  };
+  for (int c = threadIdx.x; c < wq; c += blockDim.x)
+    q[(size_t)t * q_stride + c] = from_float<T>(turned(xq, q_norm_w, inv_q, c / dk, c % dk));
+  if (k == nullptr) return;
+  const int page = LLMRS_CHECKED_PAGE(block_table[(size_t)token_req[t] * table_stride + pos / page_size], 2, t);
+  const int slot = pos % page_size;
+  for (int c = threadIdx.x; c < wk; c += blockDim.x) {
+    const int head = c / dk, i = c % dk;
+    cache[page_head_offset(page, head, n_kv_heads, page_size, dk, dv) + (size_t)slot * dk + i] =
+        from_float<T>(turned(xk, k_norm_w, inv_k, head, i));
+  }
+  for (int c = threadIdx.x; c < n_kv_heads * dv; c += blockDim.x) {
+    const int head = c / dv, i = c % dv;
+    cache[page_head_offset(page, head, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk + (size_t)slot * dv + i] =
+        v[(size_t)t * v_stride + c];
+  }
+}
+
+// q: [tokens, n_q_heads * dk] rewritten in place; k, v: the new keys and values (null: the entry reads another
+// entry's pages and writes none); cache: one entry's pages.
+LLMRS_API int llmrs_scored_prepare(void* q, long long q_stride, const void* k, long long k_stride, const void* v,
+                                   long long v_stride, int dtype, const float* q_norm_w, const float* k_norm_w,
+                                   const double* inv_freq, const int* positions, const int* token_req,
+                                   const int* block_table, int table_stride, void* cache, int n_tokens, int n_q_heads,
+                                   int n_kv_heads, int dk, int dv, int rot_dims, int page_size, float eps,
+                                   cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && n_q_heads > 0 && n_kv_heads > 0 && dk > 0 && dv > 0 && page_size > 0,
+                "scored_prepare: bad sizes");
+  LLMRS_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk, "scored_prepare: rot_dims %d of %d", rot_dims, dk);
+  if (n_tokens == 0) return 0;
+  const size_t smem = ((size_t)(n_q_heads + n_kv_heads) * dk + rot_dims) * sizeof(float);
+  LLMRS_REQUIRE(smem <= 160 * 1024, "scored_prepare: rows of %zu bytes are too wide", smem);
+  const int threads = n_q_heads * dk >= 2048 ? 512 : 256;
+#define LLMRS_SP_LAUNCH(T)                                                                                          \
+  do {                                                                                                              \
+    static size_t configured = 48 * 1024;                                                                           \
+    if (smem > configured) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(scored_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                           (int)smem);                                                              \
+      if (e != cudaSuccess) return llmrs_fail("scored_prepare: shared memory %zu: %s", smem, cudaGetErrorString(e)); \
+      configured = smem;                                                                                            \
+    }                                                                                                               \
+    scored_prepare_kernel<T><<<n_tokens, threads, smem, stream>>>(                                                  \
+        (T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, q_norm_w, k_norm_w, inv_freq, positions,     \
+        token_req, block_table, table_stride, (T*)cache, n_q_heads, n_kv_heads, dk, dv, rot_dims, page_size, eps);  \
+  } while (0)
+  if (dtype == LLMRS_F32) LLMRS_SP_LAUNCH(float);
+  else if (dtype == LLMRS_BF16) LLMRS_SP_LAUNCH(__nv_bfloat16);
+  else return llmrs_fail("scored_prepare: unknown dtype %d", dtype);
+#undef LLMRS_SP_LAUNCH
+  return llmrs_launch_status("scored_prepare");
+}
+
+// ---------------------------------------------------------------------------------
+// prefill, any type
+// ---------------------------------------------------------------------------------
+constexpr int SP_BQ = 16, SP_TILE = 64, SP_BK = 32, SP_THREADS = 256, SP_MAX_VCH = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(SP_THREADS)
+scored_prefill_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
+                      const T* __restrict__ cache, const int* __restrict__ tiles, const int* __restrict__ q_start,
+                      const int* __restrict__ n_new, const int* __restrict__ cached_len,
+                      const int* __restrict__ block_table, int table_stride, int n_q_heads, int n_kv_heads, int dk,
+                      int dv, int page_size, ScoreOpts opt) {
+  extern __shared__ float smem[];
+  float* Qs = smem;                       // [SP_BQ][dk]
+  float* Ks = Qs + SP_BQ * dk;            // [SP_BK][dk + 1]
+  float* Vs = Ks + SP_BK * (dk + 1);      // [SP_BK][dv]
+  float* Ps = Vs + SP_BK * dv;            // [SP_BQ][SP_BK]
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int kvh = head / (n_q_heads / n_kv_heads);
+  const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1] + blockIdx.z * SP_BQ;
+  if (q_off >= n_new[req]) return;
+  const int rows = min(SP_BQ, n_new[req] - q_off);
+  const int tok0 = q_start[req] + q_off;
+  const int pos0 = cached_len[req] + q_off;
+  const int kv_hi = pos0 + rows;
+  const int key_floor = first_visible(opt, pos0);       // the first row sees furthest back; pages below may be gone
+  const int kv_lo = (key_floor / SP_BK) * SP_BK;
+  const int* table = block_table + (size_t)req * table_stride;
+  const int tid = threadIdx.x, r = tid >> 4, c = tid & 15;
+
+  for (int i = tid; i < SP_BQ * dk; i += SP_THREADS) {
+    const int rr = i / dk, cc = i - rr * dk;
+    Qs[i] = rr < rows ? to_float(q[(size_t)(tok0 + rr) * q_stride + (size_t)head * dk + cc]) : 0.f;
+  }
+  float acc[SP_MAX_VCH];
+#pragma unroll
+  for (int j = 0; j < SP_MAX_VCH; ++j) acc[j] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  const int my_pos = pos0 + r;
+  const int my_lo = first_visible(opt, my_pos);
+
+  for (int kb = kv_lo; kb < kv_hi; kb += SP_BK) {
+    __syncthreads();
+    for (int i = tid; i < SP_BK * dk; i += SP_THREADS) {
+      const int kk = i / dk, cc = i - kk * dk, key = kb + kk;
+      float kf = 0.f;
+      if (key >= key_floor && key < kv_hi) {
+        const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 3, key);
+        kf = to_float(cache[page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)(key % page_size) * dk + cc]);
+      }
+      Ks[kk * (dk + 1) + cc] = kf;
+    }
+    for (int i = tid; i < SP_BK * dv; i += SP_THREADS) {
+      const int kk = i / dv, cc = i - kk * dv, key = kb + kk;
+      float vf = 0.f;
+      if (key >= key_floor && key < kv_hi) {
+        const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 3, key);
+        vf = to_float(cache[page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk +
+                            (size_t)(key % page_size) * dv + cc]);
+      }
+      Vs[kk * dv + cc] = vf;
+    }
+    __syncthreads();
+    float s[SP_BK / 16];
+#pragma unroll
+    for (int jj = 0; jj < SP_BK / 16; ++jj) {
+      const int kk = c + 16 * jj, key = kb + kk;
+      const float* qr = Qs + r * dk;
+      const float* kr = Ks + kk * (dk + 1);
+      float dot = 0.f;
+      for (int e = 0; e < dk; ++e) dot = fmaf(qr[e], kr[e], dot);
+      const bool seen = r < rows && key <= my_pos && key >= my_lo;
+      s[jj] = seen ? capped(opt, dot) : -INFINITY;
+    }
+    float bm = s[0];
+#pragma unroll
+    for (int jj = 1; jj < SP_BK / 16; ++jj) bm = fmaxf(bm, s[jj]);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o, 16));
+    const float m_new = fmaxf(m, bm);
+    float corr = 1.f, bs = 0.f;
+    if (m_new > -INFINITY) {
+      corr = expf(m - m_new);
+#pragma unroll
+      for (int jj = 0; jj < SP_BK / 16; ++jj) {
+        const float p = expf(s[jj] - m_new);
+        Ps[r * SP_BK + c + 16 * jj] = p;
+        bs += p;
+      }
+    } else {
+#pragma unroll
+      for (int jj = 0; jj < SP_BK / 16; ++jj) Ps[r * SP_BK + c + 16 * jj] = 0.f;
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o, 16);
+    l = l * corr + bs;
+    m = m_new;
+    __syncwarp();
+    const float* pr = Ps + r * SP_BK;
+#pragma unroll
+    for (int j = 0; j < SP_MAX_VCH; ++j) {
+      const int col = c + 16 * j;
+      if (col < dv) {
+        float a = acc[j] * corr;
+        for (int kk = 0; kk < SP_BK; ++kk) a = fmaf(pr[kk], Vs[kk * dv + col], a);
+        acc[j] = a;
+      }
+    }
+  }
+  if (r < rows) {
+    float w = 1.0f;
+    if (opt.sink) {
+      const float sk = opt.sink[head], mf = fmaxf(m, sk);
+      w = expf(m - mf);
+      l = l * w + expf(sk - mf);
+    }
+    const float inv = l > 0.f ? w / l : 0.f;
+    T* o = out + (size_t)(tok0 + r) * out_stride + (size_t)head * dv;
+#pragma unroll
+    for (int j = 0; j < SP_MAX_VCH; ++j)
+      if (c + 16 * j < dv) o[c + 16 * j] = from_float<T>(acc[j] * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// prefill on the tensor cores: bfloat16, 64 queries per block (16 per warp), 64 keys per tile, two stages.
+// ---------------------------------------------------------------------------------
+using bf16 = __nv_bfloat16;
+constexpr int SM_BQ = 64, SM_BK = 64, SM_WARPS = 4, SM_THREADS = SM_WARPS * 32;
+
+template <int KCH, int VCH>
+__global__ void __launch_bounds__(SM_THREADS)
+scored_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
+                          const bf16* __restrict__ cache, const int* __restrict__ tiles,
+                          const int* __restrict__ q_start, const int* __restrict__ n_new,
+                          const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
+                          int n_q_heads, int n_kv_heads, int page_size, ScoreOpts opt) {
+  constexpr int DK = 16 * KCH, DV = 16 * VCH, KROW = DK + 8, VROW = DV + 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* KV = reinterpret_cast<bf16*>(smem_raw);     // 2 stages x (K [64][KROW], V [64][VROW])
+  constexpr int STAGE = SM_BK * (KROW + VROW);
+  // The last tiles of a prompt see the most keys: they start first.
+  const int head = blockIdx.x % n_q_heads;
+  const int tile = (int)(gridDim.x / n_q_heads) - 1 - (int)(blockIdx.x / n_q_heads);
+  const int kvh = head / (n_q_heads / n_kv_heads);
+  const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1];
+  const int rows = min(SM_BQ, n_new[req] - q_off);
+  const int tok0 = q_start[req] + q_off;
+  const int pos0 = cached_len[req] + q_off;
+  const int kv_hi = pos0 + rows;
+  const int key_floor = first_visible(opt, pos0);        // no row reads a key below this
+  const int kv_lo = (key_floor / SM_BK) * SM_BK;
+  const int* table = block_table + (size_t)req * table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+
+  auto load_kv = [&](int kb, int stage) {
+    bf16* Ks = KV + (size_t)stage * STAGE;
+    bf16* Vs = Ks + SM_BK * KROW;
+    for (int c = threadIdx.x; c < SM_BK * (DK / 8); c += SM_THREADS) {
+      const int row = c / (DK / 8), ch = c - row * (DK / 8), key = kb + row;
+      const bool valid = key >= key_floor && key < kv_hi;
+      const bf16* src = cache;
+      if (valid) {
+        const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 4, key);
+        src = cache + page_head_offset(page, kvh, n_kv_heads, page_size, DK, DV) + (size_t)(key % page_size) * DK + ch * 8;
+      }
+      cp_async_16(Ks + row * KROW + ch * 8, src, valid ? 16 : 0);
+    }
+    for (int c = threadIdx.x; c < SM_BK * (DV / 8); c += SM_THREADS) {
+      const int row = c / (DV / 8), ch = c - row * (DV / 8), key = kb + row;
+      const bool valid = key >= key_floor && key < kv_hi;
+      const bf16* src = cache;
+      if (valid) {
+        const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 4, key);
+        src = cache + page_head_offset(page, kvh, n_kv_heads, page_size, DK, DV) + (size_t)page_size * DK +
+              (size_t)(key % page_size) * DV + ch * 8;
+      }
+      cp_async_16(Vs + row * VROW + ch * 8, src, valid ? 16 : 0);
+    }
+  };
+  load_kv(kv_lo, 0);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  uint32_t qf[KCH][4];
+  {
+    const int r0 = warp * 16 + gq, r1 = r0 + 8;
+    const bf16* q0 = q + (size_t)(tok0 + r0) * q_stride + (size_t)head * DK;
+    const bf16* q1 = q + (size_t)(tok0 + r1) * q_stride + (size_t)head * DK;
+#pragma unroll
+    for (int kc = 0; kc < KCH; ++kc) {
+      const int col = kc * 16 + tq * 2;
+      qf[kc][0] = r0 < rows ? *reinterpret_cast<const uint32_t*>(q0 + col) : 0u;
+      qf[kc][1] = r1 < rows ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
+      qf[kc][2] = r0 < rows ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
+      qf[kc][3] = r1 < rows ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
+    }
+  }
+  float o[2 * VCH][4];
+#pragma unroll
+  for (int n = 0; n < 2 * VCH; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+  const int pos_r[2] = {pos0 + warp * 16 + gq, pos0 + warp * 16 + gq + 8};
+  const int lo_r[2] = {first_visible(opt, pos_r[0]), first_visible(opt, pos_r[1])};
+  const int warp_lo = first_visible(opt, pos0 + warp * 16);      // first_visible never falls as the position grows
+  constexpr float LOG2E = 1.4426950408889634f;
+
+  int stage = 0;
+  for (int kb = kv_lo; kb < kv_hi; kb += SM_BK, stage ^= 1) {
+    if (kb + SM_BK < kv_hi) load_kv(kb + SM_BK, stage ^ 1);
+    cp_async_commit();
+    const bf16* Ks = KV + (size_t)stage * STAGE;
+    const bf16* Vs = Ks + SM_BK * KROW;
+    // A warp whose rows all lie before this tile, or whose rows all start after it, has nothing to add.
+    const bool active = kb <= pos0 + warp * 16 + 15 && kb + SM_BK > warp_lo;
+    if (active) {
+      float s[SM_BK / 8][4];
+#pragma unroll
+      for (int n = 0; n < SM_BK / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+      for (int kc = 0; kc < KCH; ++kc) {
+        const int j = lane >> 3;
+#pragma unroll
+        for (int np = 0; np < SM_BK / 16; ++np) {
+          uint32_t b[4];
+          ldmatrix_x4(b, Ks + (np * 16 + (j >> 1) * 8 + (lane & 7)) * KROW + kc * 16 + (j & 1) * 8);
+          mma_bf16_16816(s[2 * np], qf[kc], b[0], b[1]);
+          mma_bf16_16816(s[2 * np + 1], qf[kc], b[2], b[3]);
+        }
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < SM_BK / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kb + n * 8 + tq * 2 + (e & 1);
+          const bool seen = key <= pos_r[e >> 1] && key >= lo_r[e >> 1];
+          s[n][e] = seen ? capped(opt, s[n][e]) * LOG2E : -INFINITY;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+        }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_row[r], mx[r]);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        corr[r] = exp2f(m_row[r] - m_use);
+        m_row[r] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < SM_BK / 8; ++n)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float p = exp2f(s[n][r * 2 + e] - m_use);
+            s[n][r * 2 + e] = p;
+            sum += p;
+          }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_row[r] = l_row[r] * corr[r] + sum;
+      }
+#pragma unroll
+      for (int n = 0; n < 2 * VCH; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kc = 0; kc < SM_BK / 16; ++kc) {
+        uint32_t pf[4];
+        pf[0] = pack_bf16(s[2 * kc][0], s[2 * kc][1]);
+        pf[1] = pack_bf16(s[2 * kc][2], s[2 * kc][3]);
+        pf[2] = pack_bf16(s[2 * kc + 1][0], s[2 * kc + 1][1]);
+        pf[3] = pack_bf16(s[2 * kc + 1][2], s[2 * kc + 1][3]);
+        const int j = lane >> 3;
+#pragma unroll
+        for (int nc = 0; nc < VCH; ++nc) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, Vs + (kc * 16 + (j & 1) * 8 + (lane & 7)) * VROW + (2 * nc + (j >> 1)) * 8);
+          mma_bf16_16816(o[2 * nc], pf, b[0], b[1]);
+          mma_bf16_16816(o[2 * nc + 1], pf, b[2], b[3]);
+        }
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + gq + r * 8;
+    if (row < rows) {
+      float w = 1.0f, l = l_row[r];
+      if (opt.sink) {
+        const float sk = opt.sink[head] * LOG2E, mf = fmaxf(m_row[r], sk);
+        w = exp2f(m_row[r] - mf);
+        l = l * w + exp2f(sk - mf);
+      }
+      const float inv = l > 0.f ? w / l : 0.f;
+      bf16* orow = out + (size_t)(tok0 + row) * out_stride + (size_t)head * DV;
+#pragma unroll
+      for (int n = 0; n < 2 * VCH; ++n)
+        *reinterpret_cast<__nv_bfloat162*>(orow + n * 8 + tq * 2) =
+            __floats2bfloat162_rn(o[n][r * 2] * inv, o[n][r * 2 + 1] * inv);
+    }
+  }
+}
+
+template <int KCH, int VCH>
+static int launch_scored_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* cache,
+                             const int* tiles, int n_tiles, const int* q_start, const int* n_new,
+                             const int* cached_len, const int* block_table, int table_stride, int n_q_heads,
+                             int n_kv_heads, int page_size, const ScoreOpts& opt, cudaStream_t stream) {
+  const size_t smem = (size_t)2 * SM_BK * (16 * KCH + 8 + 16 * VCH + 8) * sizeof(bf16);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(scored_prefill_mma_kernel<KCH, VCH>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("scored_prefill_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = smem;
+  }
+  dim3 grid((unsigned)n_tiles * (unsigned)n_q_heads);
+  scored_prefill_mma_kernel<KCH, VCH><<<grid, SM_THREADS, smem, stream>>>(
+      (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, tiles, q_start, n_new, cached_len,
+      block_table, table_stride, n_q_heads, n_kv_heads, page_size, opt);
+  return llmrs_launch_status("scored_prefill_mma");
+}
+
+static int g_scored_generic_only = 0;
+// 1: bfloat16 also takes the kernel for any type (tests compare the two).
+LLMRS_API void llmrs_scored_generic_only(int on) { g_scored_generic_only = on; }
+
+// Head sizes the tensor-core kernel is built for (keys, values), in units of 16.
+#define LLMRS_SCORED_MMA_SIZES(X)                                                                              \
+  X(1, 1) X(2, 2) X(3, 3) X(4, 4) X(5, 5) X(6, 6) X(7, 7) X(8, 8) X(1, 2) X(2, 1) X(2, 3) X(3, 2) X(2, 4) X(4, 2) \
+  X(3, 4) X(4, 3) X(4, 6) X(6, 4) X(4, 8) X(8, 4) X(6, 8) X(8, 6) X(12, 8)
+
+LLMRS_API int llmrs_scored_prefill(const void* q, long long q_stride, void* out, long long out_stride,
+                                   const void* cache, const int* tiles, int n_tiles, const int* q_start,
+                                   const int* n_new, const int* cached_len, const int* block_table, int table_stride,
+                                   int n_q_heads, int n_kv_heads, int dk, int dv, int page_size, float scale,
+                                   float softcap, const float* sink, int mask, int mask_size, int dtype,
+                                   cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tiles >= 0 && n_q_heads > 0 && n_kv_heads > 0 && page_size > 0, "scored_prefill: bad sizes");
+  LLMRS_REQUIRE(n_q_heads % n_kv_heads == 0, "scored_prefill: %d query heads are no multiple of %d key heads",
+                n_q_heads, n_kv_heads);
+  LLMRS_REQUIRE(dk >= 1 && dk <= 256 && dv >= 1 && dv <= 16 * SP_MAX_VCH, "scored_prefill: head sizes %d / %d (1..256)",
+                dk, dv);
+  LLMRS_REQUIRE(mask == MASK_CAUSAL || ((mask == MASK_WINDOW || mask == MASK_CHUNK) && mask_size > 0),
+                "scored_prefill: mask %d with size %d", mask, mask_size);
+  if (n_tiles == 0) return 0;
+  ScoreOpts opt{scale, softcap, sink, mask, mask_size};
+  if ((long long)n_tiles * n_q_heads > 2147483647LL) return llmrs_fail("scored_prefill: %d tiles are too many", n_tiles);
+  if (dtype == LLMRS_BF16 && !g_scored_generic_only && q_stride % 2 == 0 && out_stride % 2 == 0) {
+#define LLMRS_SM_CASE(K, V)                                                                                     \
+  if (dk == 16 * K && dv == 16 * V)                                                                              \
+    return launch_scored_mma<K, V>(q, q_stride, out, out_stride, cache, tiles, n_tiles, q_start, n_new,         \
+                                   cached_len, block_table, table_stride, n_q_heads, n_kv_heads, page_size, opt, \
+                                   stream);
+    LLMRS_SCORED_MMA_SIZES(LLMRS_SM_CASE)
+#undef LLMRS_SM_CASE
+  }
+  const size_t smem = (size_t)(SP_BQ * dk + SP_BK * (dk + 1) + SP_BK * dv + SP_BQ * SP_BK) * sizeof(float);
+  dim3 grid(n_tiles, n_q_heads, SP_TILE / SP_BQ);
+#define LLMRS_SPF_LAUNCH(T)                                                                                          \
+  do {                                                                                                               \
+    static size_t configured = 48 * 1024;                                                                            \
+    if (smem > configured) {                                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(scored_prefill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                           (int)smem);                                                               \
+      if (e != cudaSuccess) return llmrs_fail("scored_prefill: shared memory %zu: %s", smem, cudaGetErrorString(e)); \
+      configured = smem;                                                                                             \
+    }                                                                                                                \
+    scored_prefill_kernel<T><<<grid, SP_THREADS, smem, stream>>>(                                                    \
+        (const T*)q, q_stride, (T*)out, out_stride, (const T*)cache, tiles, q_start, n_new, cached_len, block_table, \
+        table_stride, n_q_heads, n_kv_heads, dk, dv, page_size, opt);                                                \
+  } while (0)
+  if (dtype == LLMRS_F32) LLMRS_SPF_LAUNCH(float);
+  else if (dtype == LLMRS_BF16) LLMRS_SPF_LAUNCH(__nv_bfloat16);
+  else return llmrs_fail("scored_prefill: unknown dtype %d", dtype);
+#undef LLMRS_SPF_LAUNCH
+  return llmrs_launch_status("scored_prefill");
+}
+
+// ---------------------------------------------------------------------------------
+// decode
+// ---------------------------------------------------------------------------------
+constexpr int SD_WARPS = 4, SD_THREADS = SD_WARPS * 32, SD_MAXC = 8;      // channels per lane: head sizes up to 256
+
+__host__ __device__ inline size_t sd_part_stride(int dv) { return (size_t)dv + 2; }
+
+// One block per (decode request, query head, run of keys). Each warp takes every fourth key of the run: its lanes
+// split the channels, the dot product is summed over the warp, the weights and the sum of values are kept online.
+template <typename T>
+__global__ void __launch_bounds__(SD_THREADS)
+scored_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ cache,
+                     const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
+                     const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
+                     float* __restrict__ part, int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int dk,
+                     int dv, int page_size, ScoreOpts opt) {
+  __shared__ float s_m[SD_WARPS], s_l[SD_WARPS];
+  extern __shared__ float s_o[];      // [SD_WARPS][dv]
+  const int di = blockIdx.x, head = blockIdx.y, split = blockIdx.z;
+  const int kvh = head / (n_q_heads / n_kv_heads);
+  const int req = dec_reqs[di];
+  const int pos = cached_len[req];                  // the new token's key is in the cache already
+  const int lo = first_visible(opt, pos);
+  const int k_begin = lo + split * split_keys, k_end = min(k_begin + split_keys, pos + 1);
+  float* pp = part + (((size_t)di * n_q_heads + head) * max_splits + split) * sd_part_stride(dv);
+  if (k_begin >= k_end) {
+    if (threadIdx.x == 0) { pp[0] = -INFINITY; pp[1] = 0.f; }
+    return;
+  }
+  const int* table = block_table + (size_t)req * table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float qr[SD_MAXC], acc[SD_MAXC];
+  const T* qp = q + (size_t)q_start[req] * q_stride + (size_t)head * dk;
+#pragma unroll
+  for (int j = 0; j < SD_MAXC; ++j) {
+    qr[j] = lane + 32 * j < dk ? to_float(qp[lane + 32 * j]) : 0.f;
+    acc[j] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int key = k_begin + warp; key < k_end; key += SD_WARPS) {
+    const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 3, key);
+    const T* kr = cache + page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)(key % page_size) * dk;
+    const T* vr = cache + page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk +
+                  (size_t)(key % page_size) * dv;
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < SD_MAXC; ++j)
+      if (lane + 32 * j < dk) dot = fmaf(qr[j], to_float(kr[lane + 32 * j]), dot);
+    const float s = capped(opt, warp_sum(dot));
+    const float m_new = fmaxf(m, s), corr = expf(m - m_new), p = expf(s - m_new);
+    l = l * corr + p;
+    m = m_new;
+#pragma unroll
+    for (int j = 0; j < SD_MAXC; ++j)
+      if (lane + 32 * j < dv) acc[j] = fmaf(p, to_float(vr[lane + 32 * j]), acc[j] * corr);
+  }
+  if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+  for (int j = 0; j < SD_MAXC; ++j)
+    if (lane + 32 * j < dv) s_o[warp * dv + lane + 32 * j] = acc[j];
+  __syncthreads();
+  float mm = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < SD_WARPS; ++w) mm = fmaxf(mm, s_m[w]);
+  for (int c = threadIdx.x; c < dv; c += SD_THREADS) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w) a += s_m[w] == -INFINITY ? 0.f : s_o[w * dv + c] * expf(s_m[w] - mm);
+    pp[2 + c] = a;
+  }
+  if (threadIdx.x == 0) {
+    float ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w) ll += s_m[w] == -INFINITY ? 0.f : s_l[w] * expf(s_m[w] - mm);
+    pp[0] = mm;
+    pp[1] = ll;
+  }
+}
+
+template <typename T>
+__global__ void scored_decode_merge_kernel(const float* __restrict__ part, T* __restrict__ out, long long out_stride,
+                                           const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
+                                           int max_splits, int n_q_heads, int dv, const float* __restrict__ sink) {
+  const int di = blockIdx.x, head = blockIdx.y;
+  const float* base = part + ((size_t)di * n_q_heads + head) * max_splits * sd_part_stride(dv);
+  float m = sink ? sink[head] : -INFINITY;
+  for (int s = 0; s < max_splits; ++s) m = fmaxf(m, base[(size_t)s * sd_part_stride(dv)]);
+  float l = sink ? expf(sink[head] - m) : 0.f;
+  for (int s = 0; s < max_splits; ++s) {
+    const float* pp = base + (size_t)s * sd_part_stride(dv);
+    if (pp[0] > -INFINITY) l += pp[1] * expf(pp[0] - m);
+  }
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  T* o = out + (size_t)q_start[dec_reqs[di]] * out_stride + (size_t)head * dv;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < max_splits; ++s) {
+      const float* pp = base + (size_t)s * sd_part_stride(dv);
+      if (pp[0] > -INFINITY) a += pp[2 + c] * expf(pp[0] - m);
+    }
+    o[c] = from_float<T>(a * inv);
+  }
+}
+
+LLMRS_API long long llmrs_scored_decode_scratch_floats(int n_dec, int n_q_heads, int dv, int max_splits) {
+  return (long long)n_dec * n_q_heads * max_splits * (long long)sd_part_stride(dv);
+}
+
+// `max_splits` runs of `split_keys` keys, counted from each request's first visible key, must cover the longest
+// visible span; scratch holds llmrs_scored_decode_scratch_floats floats.
+LLMRS_API int llmrs_scored_decode(const void* q, long long q_stride, void* out, long long out_stride,
+                                  const void* cache, const int* dec_reqs, int n_dec, const int* q_start,
+                                  const int* cached_len, const int* block_table, int table_stride, float* scratch,
+                                  int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int dk, int dv,
+                                  int page_size, float scale, float softcap, const float* sink, int mask,
+                                  int mask_size, int dtype, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_dec >= 0 && n_q_heads > 0 && n_kv_heads > 0 && page_size > 0 && max_splits > 0 && split_keys > 0,
+                "scored_decode: bad sizes");
+  LLMRS_REQUIRE(n_q_heads % n_kv_heads == 0, "scored_decode: %d query heads are no multiple of %d key heads",
+                n_q_heads, n_kv_heads);
+  LLMRS_REQUIRE(dk >= 1 && dk <= 32 * SD_MAXC && dv >= 1 && dv <= 32 * SD_MAXC, "scored_decode: head sizes %d / %d", dk, dv);
+  LLMRS_REQUIRE(mask == MASK_CAUSAL || ((mask == MASK_WINDOW || mask == MASK_CHUNK) && mask_size > 0),
+                "scored_decode: mask %d with size %d", mask, mask_size);
+  LLMRS_REQUIRE(n_q_heads <= 65535 && max_splits <= 65535, "scored_decode: too many heads or runs");
+  if (n_dec == 0) return 0;
+  ScoreOpts opt{scale, softcap, sink, mask, mask_size};
+  dim3 grid(n_dec, n_q_heads, max_splits), mgrid(n_dec, n_q_heads);
+  const size_t smem = (size_t)SD_WARPS * dv * sizeof(float);
+  if (dtype == LLMRS_F32) {
+    scored_decode_kernel<float><<<grid, SD_THREADS, smem, stream>>>(
+        (const float*)q, q_stride, (const float*)cache, dec_reqs, q_start, cached_len, block_table, table_stride,
+        scratch, max_splits, split_keys, n_q_heads, n_kv_heads, dk, dv, page_size, opt);
+    int rc = llmrs_launch_status("scored_decode");
+    if (rc) return rc;
+    scored_decode_merge_kernel<float><<<mgrid, 64, 0, stream>>>(scratch, (float*)out, out_stride, dec_reqs, q_start,
+                                                                max_splits, n_q_heads, dv, sink);
+  } else if (dtype == LLMRS_BF16) {
+    scored_decode_kernel<bf16><<<grid, SD_THREADS, smem, stream>>>(
+        (const bf16*)q, q_stride, (const bf16*)cache, dec_reqs, q_start, cached_len, block_table, table_stride,
+        scratch, max_splits, split_keys, n_q_heads, n_kv_heads, dk, dv, page_size, opt);
+    int rc = llmrs_launch_status("scored_decode");
+    if (rc) return rc;
+    scored_decode_merge_kernel<bf16><<<mgrid, 64, 0, stream>>>(scratch, (bf16*)out, out_stride, dec_reqs, q_start,
+                                                               max_splits, n_q_heads, dv, sink);
+  } else {
+    return llmrs_fail("scored_decode: unknown dtype %d", dtype);
+  }
+  return llmrs_launch_status("scored_decode (merge)");
+}

@@ -9,8 +9,9 @@
 
 constexpr int GF_BM = 64, GF_BN = 64, GF_BK = 16, GF_THREADS = 256;
 
+template <typename TX>
 __global__ void __launch_bounds__(GF_THREADS)
-gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+gemm_f32_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
                 float* __restrict__ out, int M, int N, int K, long long x_stride, long long out_stride) {
   __shared__ float As[GF_BK][GF_BM + 4];
   __shared__ float Bs[GF_BK][GF_BN + 4];
@@ -30,7 +31,7 @@ gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const 
     for (int e = 0; e < 4; ++e) {
       const int k = k0 + lk + e;
       const int m = m0 + lrow, n = n0 + lrow;
-      As[lk + e][lrow] = (m < M && k < K) ? x[(size_t)m * x_stride + k] : 0.f;
+      As[lk + e][lrow] = (m < M && k < K) ? to_float(x[(size_t)m * x_stride + k]) : 0.f;
       Bs[lk + e][lrow] = (n < N && k < K) ? w[(size_t)n * K + k] : 0.f;
     }
     __syncthreads();
@@ -66,6 +67,20 @@ LLMRS_API int llmrs_gemm_f32(const float* x, long long x_stride, const float* w,
   if (M == 0) return 0;
   dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
   LLMRS_REQUIRE(grid.y <= 65535, "gemm_f32: M=%d is too large", M);
-  gemm_f32_kernel<<<grid, GF_THREADS, 0, stream>>>(x, w, bias, out, M, N, K, x_stride, out_stride);
+  gemm_f32_kernel<float><<<grid, GF_THREADS, 0, stream>>>(x, w, bias, out, M, N, K, x_stride, out_stride);
   return llmrs_launch_status("gemm_f32");
+}
+
+// The same product for rows stored in bfloat16 (activations of the bfloat16 path whose product must not be rounded:
+// a router's logits, the gates of a recurrence): the rows are widened as they are read, weights, sums and output
+// are float32.
+LLMRS_API int llmrs_gemm_f32_bf16_rows(const void* x, long long x_stride, const float* w, const float* bias, float* out,
+                                       long long out_stride, int M, int N, int K, cudaStream_t stream) {
+  LLMRS_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_f32: bad sizes M=%d N=%d K=%d", M, N, K);
+  if (M == 0) return 0;
+  dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
+  LLMRS_REQUIRE(grid.y <= 65535, "gemm_f32: M=%d is too large", M);
+  gemm_f32_kernel<__nv_bfloat16><<<grid, GF_THREADS, 0, stream>>>((const __nv_bfloat16*)x, w, bias, out, M, N, K,
+                                                                  x_stride, out_stride);
+  return llmrs_launch_status("gemm_f32 (bfloat16 rows)");
 }

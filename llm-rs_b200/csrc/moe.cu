@@ -153,3 +153,100 @@ LLMRS_API int llmrs_moe_combine(const float* rows, const int* row_of, const floa
     return llmrs_fail("moe_combine: unknown dtype %d", out_dtype);
   return llmrs_launch_status("moe_combine");
 }
+
+// ---------------------------------------------------------------------------------
+// Router "linear": the `top` largest of a token's logits (float32, made by a product before this kernel), weighted
+// by the softmax over the chosen logits only. One warp per token; the lanes hold the logits strided and pick the
+// largest `top` times (among equal logits the lower expert wins), so the assignments come in order of falling logit.
+// ---------------------------------------------------------------------------------
+constexpr int ROUTE_PER_LANE = 8;      // up to 256 experts
+
+__global__ void moe_route_top_kernel(const float* __restrict__ logits, long long stride, int* __restrict__ expert_of,
+                                     float* __restrict__ weight_of, int n_tokens, int n_experts, int top) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tokens) return;
+  float z[ROUTE_PER_LANE];
+#pragma unroll
+  for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+    const int e = lane + 32 * j;
+    z[j] = e < n_experts ? logits[(size_t)t * stride + e] : -INFINITY;
+  }
+  float first = 0.f, sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+      const int e = lane + 32 * j;
+      if (e < n_experts && (z[j] > best || (z[j] == best && e < at)) && z[j] != -INFINITY) { best = z[j]; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at == 0x7fffffff) at = k;      // logits that are no numbers: any expert, weight 0
+#pragma unroll
+    for (int j = 0; j < ROUTE_PER_LANE; ++j)
+      if (lane + 32 * j == at) z[j] = -INFINITY;
+    if (k == 0) first = best;
+    const float p = expf(best - first);       // the first pick is the largest: no overflow
+    sum += p;
+    if (lane == 0) {
+      expert_of[(size_t)t * top + k] = at;
+      weight_of[(size_t)t * top + k] = p;
+    }
+  }
+  __syncwarp();
+  if (lane < top) weight_of[(size_t)t * top + lane] /= sum;
+  for (int k = 32 + lane; k < top; k += 32) weight_of[(size_t)t * top + k] /= sum;
+}
+
+LLMRS_API int llmrs_moe_route_top(const float* logits, long long stride, int* expert_of, float* weight_of,
+                                  int n_tokens, int n_experts, int top, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && top > 0 && top <= n_experts, "moe_route_top: bad sizes");
+  LLMRS_REQUIRE(n_experts <= 32 * ROUTE_PER_LANE, "moe_route_top: at most %d experts, got %d", 32 * ROUTE_PER_LANE,
+                n_experts);
+  if (n_tokens == 0) return 0;
+  moe_route_top_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(logits, stride, expert_of, weight_of, n_tokens,
+                                                              n_experts, top);
+  return llmrs_launch_status("moe_route_top");
+}
+
+// ---------------------------------------------------------------------------------
+// moe_combine plus an expert that every token uses:
+// out[t, :] = sum_k weight_of[t, k] * rows[row_of[t, k], :] + sigmoid(gate[t]) * shared[t, :]   (gate null: factor 1)
+// ---------------------------------------------------------------------------------
+template <typename TS>
+__global__ void moe_combine_shared_kernel(const float* __restrict__ rows, const int* __restrict__ row_of,
+                                          const float* __restrict__ weight_of, const TS* __restrict__ shared,
+                                          const float* __restrict__ gate, long long gate_stride,
+                                          float* __restrict__ out, int top, int width) {
+  const int t = blockIdx.x;
+  const float g = shared == nullptr ? 0.f : (gate ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride])) : 1.0f);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < top; ++k)
+      s = fmaf(weight_of[t * top + k], rows[(size_t)row_of[t * top + k] * width + c], s);
+    if (shared) s = fmaf(g, to_float(shared[(size_t)t * width + c]), s);
+    out[(size_t)t * width + c] = s;
+  }
+}
+
+LLMRS_API int llmrs_moe_combine_shared(const float* rows, const int* row_of, const float* weight_of,
+                                       const void* shared, int shared_dtype, const float* gate, long long gate_stride,
+                                       float* out, int n_tokens, int top, int width, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && top > 0 && width > 0, "moe_combine_shared: bad sizes");
+  if (n_tokens == 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (shared == nullptr || shared_dtype == LLMRS_F32)
+    moe_combine_shared_kernel<float><<<n_tokens, threads, 0, stream>>>(rows, row_of, weight_of, (const float*)shared,
+                                                                       gate, gate_stride, out, top, width);
+  else if (shared_dtype == LLMRS_BF16)
+    moe_combine_shared_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        rows, row_of, weight_of, (const __nv_bfloat16*)shared, gate, gate_stride, out, top, width);
+  else
+    return llmrs_fail("moe_combine_shared: unknown dtype %d", shared_dtype);
+  return llmrs_launch_status("moe_combine_shared");
+}

@@ -68,6 +68,9 @@ class StepContext:
         self.want_rows = None
         self.block_tables: List[Optional[torch.Tensor]] = []
         self.plans: Dict[Hashable, PlanView] = {}
+        # (stream, its rows rounded to the activation type): left by a block whose last norm made the copy anyway,
+        # for the block after it.
+        self.stream_copy = None
         # Host copies, for parts that plan their work on the host.
         self.host_n_new: List[int] = []
         self.host_cached_len: List[int] = []

@@ -146,8 +146,9 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, block: i
 
 def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
              out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """True float32 ``x @ w.T (+ bias)`` with ``w`` of shape [N, K] (FFMA, no TF32)."""
-    _need(x, "x", torch.float32, contiguous=False)
+    """True float32 ``x @ w.T (+ bias)`` with ``w`` of shape [N, K] (FFMA, no TF32). ``x`` may be bfloat16 rows: they
+    are widened as they are read; weights, sums and the result stay float32."""
+    _need(x, "x", contiguous=False)
     _need(w, "w", torch.float32)
     M, K = x.shape
     N = w.size(0)
@@ -158,8 +159,10 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = No
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
     _need(out, "out", torch.float32, contiguous=False)
-    _check(_lib().llmrs_gemm_f32(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(bias), _ptr(out),
-                                 ctypes.c_longlong(_row_stride(out, "out")), M, N, K, _stream()), "gemm_f32")
+    fn = _lib().llmrs_gemm_f32 if x.dtype == torch.float32 else _lib().llmrs_gemm_f32_bf16_rows
+    dtype_code(x.dtype)     # refuses any other type
+    _check(fn(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(bias), _ptr(out),
+              ctypes.c_longlong(_row_stride(out, "out")), M, N, K, _stream()), "gemm_f32")
     return out
 
 
@@ -943,3 +946,191 @@ def latent_attention_prefill(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tens
         return False
     _check(rc, "latent_attention_prefill")
     return True
+
+
+# -- blocks that norm after the residual sum; small element-wise kernels -----------------------------------
+def post_norm(h: torch.Tensor, y: Optional[torch.Tensor], layer_scale: Optional[torch.Tensor], weight: torch.Tensor,
+              alpha: float, eps: float, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """``h = rms(alpha * h + y * layer_scale) * weight`` row by row, in place on the float32 stream ``h`` (``y`` and
+    ``layer_scale`` may be None). With ``out_dtype`` the rows are also returned rounded to that type."""
+    _need(h, "h", torch.float32)
+    _need(weight, "weight", torch.float32)
+    if y is not None:
+        _need(y, "y")
+        if y.shape != h.shape:
+            raise KernelError(f"post_norm: h {tuple(h.shape)}, y {tuple(y.shape)}")
+    if layer_scale is not None:
+        _need(layer_scale, "layer_scale", torch.float32)
+    if weight.numel() != h.size(1) or (layer_scale is not None and layer_scale.numel() != h.size(1)):
+        raise KernelError(f"post_norm: rows of {h.size(1)}, weight {weight.numel()}")
+    out = None if out_dtype is None else torch.empty(tuple(h.shape), dtype=out_dtype, device=h.device)
+    _check(_lib().llmrs_post_norm(
+        _ptr(h), _ptr(y), dtype_code(y.dtype) if y is not None else F32, _ptr(layer_scale), _ptr(weight), _ptr(out),
+        dtype_code(out_dtype) if out_dtype is not None else F32, h.size(0), h.size(1), ctypes.c_float(alpha),
+        ctypes.c_float(eps), _stream()), "post_norm")
+    return out
+
+
+def relu_sq(x: torch.Tensor) -> torch.Tensor:
+    """``max(x, 0)^2`` element by element."""
+    _need(x, "x")
+    out = torch.empty_like(x)
+    _check(_lib().llmrs_relu_sq(_ptr(x), _ptr(out), _LL(x.numel()), dtype_code(x.dtype), _stream()), "relu_sq")
+    return out
+
+
+def scale_(z: torch.Tensor, s: float) -> torch.Tensor:
+    """``z *= s`` in place (float32)."""
+    _need(z, "z", torch.float32)
+    _check(_lib().llmrs_scale(_ptr(z), _LL(z.numel()), ctypes.c_float(s), _stream()), "scale")
+    return z
+
+
+# -- linear recurrences with a matrix state ---------------------------------------------------------------
+def gate_scan(gates: torch.Tensor, cap: float, m_state: torch.Tensor, ctx, n_heads: int):
+    """Exponential gates with a running maximum over a step's tokens (``csrc/linear_recurrence.cu``). ``gates``:
+    float32 [tokens, 2 * heads], the input gate's pre-activations then the forget gate's; ``m_state`` float32
+    [slots, heads], updated in place. Returns (decay, gain, floor), each float32 [tokens, heads]."""
+    _need(gates, "gates", torch.float32, contiguous=False)
+    _need(m_state, "m_state", torch.float32)
+    n = gates.size(0)
+    if gates.size(1) != 2 * n_heads or m_state.size(-1) != n_heads:
+        raise KernelError(f"gate_scan: gates {tuple(gates.shape)}, state {tuple(m_state.shape)}, {n_heads} heads")
+    decay, gain, floor = (torch.empty((n, n_heads), dtype=torch.float32, device=gates.device) for _ in range(3))
+    _check(_lib().llmrs_gate_scan(_ptr(gates), _LL(_row_stride(gates, "gates")), ctypes.c_float(cap), _ptr(m_state),
+                                  _ptr(ctx.q_start), _ptr(ctx.n_new), _ptr(ctx.slot_ids), _ptr(decay), _ptr(gain),
+                                  _ptr(floor), ctx.n_requests, n_heads, _stream()), "gate_scan")
+    return decay, gain, floor
+
+
+def linear_recurrence(q, k, v, gate, norm_w, state, ctx, n_heads: int, dk: int, dv: int, norm_eps: float,
+                      act_silu: bool = False, q_scale: float = 1.0, decay=None, head_decay=None, gain=None,
+                      normaliser=None, floor=None, den_eps: float = 0.0, per_head_norm: bool = True) -> torch.Tensor:
+    """``S_t = a_t S_(t-1) + (b_t k_t) v_t^T``, ``o_t = S_t^T q_t`` per head over a step's tokens, continued from and
+    left in ``state`` [slots, heads, dk, dv]; then the output stage (division by the normaliser, RMS norm per head or
+    over all heads, weight, sigmoid gate). q, k, v, gate: column slices of the activation type with dense rows;
+    ``decay``/``gain`` float32 [tokens, heads] or None (``head_decay`` [heads]: one decay per head; nothing: 1);
+    ``normaliser`` [slots, heads, dk] with ``floor`` [tokens, heads]: o is divided by
+    ``max(|n . q|, floor) + den_eps``. Returns [tokens, heads * dv] in the activation type."""
+    for name, t in (("q", q), ("k", k), ("v", v), ("gate", gate)):
+        _need(t, name, q.dtype, contiguous=False)
+    _need(state, "state", torch.float32)
+    n = q.size(0)
+    if q.size(1) != n_heads * dk or k.size(1) != n_heads * dk or v.size(1) != n_heads * dv or \
+            gate.size(1) != n_heads * dv or tuple(state.shape[1:]) != (n_heads, dk, dv):
+        raise KernelError(f"linear_recurrence: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, "
+                          f"state {tuple(state.shape)} for {n_heads} heads of {dk} x {dv}")
+    if (normaliser is None) != (floor is None):
+        raise KernelError("linear_recurrence: normaliser and floor come together")
+    dev = q.device
+    work = torch.empty((int(_lib_ll("llmrs_linear_recurrence_work_floats")(n, n_heads, dk, dv)),), dtype=torch.float32,
+                       device=dev)
+    o_raw = torch.empty((n, n_heads * dv), dtype=torch.float32, device=dev)
+    nq = torch.empty((n, n_heads), dtype=torch.float32, device=dev) if normaliser is not None else None
+    _check(_lib().llmrs_linear_recurrence(
+        _ptr(q), _ptr(k), _ptr(v), _LL(_row_stride(q, "q")), _LL(_row_stride(k, "k")), _LL(_row_stride(v, "v")),
+        dtype_code(q.dtype), int(act_silu), ctypes.c_float(q_scale), _ptr(decay), _ptr(head_decay), _ptr(gain),
+        _ptr(state), _ptr(normaliser), _ptr(ctx.q_start), _ptr(ctx.n_new), _ptr(ctx.slot_ids), _ptr(work),
+        _ptr(o_raw), _ptr(nq), n, ctx.n_requests, n_heads, dk, dv, _stream()), "linear_recurrence", 2)
+    out = torch.empty((n, n_heads * dv), dtype=q.dtype, device=dev)
+    _check(_lib().llmrs_recurrence_output(
+        _ptr(o_raw), _ptr(nq), _ptr(floor), ctypes.c_float(den_eps), _ptr(gate), _LL(_row_stride(gate, "gate")),
+        dtype_code(q.dtype), _ptr(norm_w), _ptr(out), n, n_heads, dv, int(per_head_norm), ctypes.c_float(norm_eps),
+        _stream()), "recurrence_output")
+    return out
+
+
+# -- attention with options on the score --------------------------------------------------------------------
+MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2
+
+
+def scored_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_norm_w, k_norm_w,
+                   inv_freq: torch.Tensor, ctx, table, cache: Optional[torch.Tensor], n_q_heads: int,
+                   n_kv_heads: int, dk: int, dv: int, rot_dims: int, page_size: int, eps: float) -> None:
+    """Norm over the whole q and k rows, rotation, q rewritten in place, k and v into the pages ``cache``
+    ([pages, kv heads, page_size * (dk + dv)]); see ``csrc/attention_scored.cu``."""
+    _need(q, "q", contiguous=False)
+    _need(inv_freq, "inv_freq", torch.float64)
+    if k is not None:
+        _need(k, "k", q.dtype, contiguous=False)
+        _need(v, "v", q.dtype, contiguous=False)
+        _need(cache, "cache", q.dtype)
+    _check(_lib().llmrs_scored_prepare(
+        _ptr(q), _LL(_row_stride(q, "q")), _ptr(k), _LL(0 if k is None else _row_stride(k, "k")), _ptr(v),
+        _LL(0 if v is None else _row_stride(v, "v")), dtype_code(q.dtype), _ptr(q_norm_w), _ptr(k_norm_w),
+        _ptr(inv_freq), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(table), 0 if table is None else table.size(1),
+        _ptr(cache), q.size(0), n_q_heads, n_kv_heads, dk, dv, rot_dims, page_size, ctypes.c_float(eps), _stream()),
+        "scored_prepare")
+
+
+def scored_generic_only(on: bool) -> None:
+    """True: bfloat16 prompt portions take the kernel for any type too (tests compare it with the tensor-core one)."""
+    fn = _lib().llmrs_scored_generic_only
+    fn.restype, fn.argtypes = None, [ctypes.c_int]
+    fn(1 if on else 0)
+
+
+def scored_prefill(q, out, cache, tiles, n_tiles: int, ctx, table, n_q_heads: int, n_kv_heads: int, dk: int, dv: int,
+                   page_size: int, scale: float, softcap: float, sink, mask: int, mask_size: int) -> None:
+    """Prompt portions (tiles of 64 queries: request, offset) through ``csrc/attention_scored.cu``."""
+    _need(q, "q", contiguous=False)
+    _need(out, "out", q.dtype, contiguous=False)
+    _need(cache, "cache", q.dtype)
+    _check(_lib().llmrs_scored_prefill(
+        _ptr(q), _LL(_row_stride(q, "q")), _ptr(out), _LL(_row_stride(out, "out")), _ptr(cache), _ptr(tiles), n_tiles,
+        _ptr(ctx.q_start), _ptr(ctx.n_new), _ptr(ctx.cached_len), _ptr(table), table.size(1), n_q_heads, n_kv_heads,
+        dk, dv, page_size, ctypes.c_float(scale), ctypes.c_float(softcap), _ptr(sink), mask, mask_size,
+        dtype_code(q.dtype), _stream()), "scored_prefill")
+
+
+def scored_decode(q, out, cache, dec_reqs, n_dec: int, ctx, table, max_splits: int, split_keys: int, n_q_heads: int,
+                  n_kv_heads: int, dk: int, dv: int, page_size: int, scale: float, softcap: float, sink, mask: int,
+                  mask_size: int) -> None:
+    """Requests that bring one token: runs of ``split_keys`` keys from each request's first visible key."""
+    _need(q, "q", contiguous=False)
+    _need(out, "out", q.dtype, contiguous=False)
+    _need(cache, "cache", q.dtype)
+    n_floats = int(_lib_ll("llmrs_scored_decode_scratch_floats")(n_dec, n_q_heads, dv, max_splits))
+    scratch = ctx.scratch("scored_decode", n_floats)
+    _check(_lib().llmrs_scored_decode(
+        _ptr(q), _LL(_row_stride(q, "q")), _ptr(out), _LL(_row_stride(out, "out")), _ptr(cache), _ptr(dec_reqs), n_dec,
+        _ptr(ctx.q_start), _ptr(ctx.cached_len), _ptr(table), table.size(1), _ptr(scratch), max_splits, split_keys,
+        n_q_heads, n_kv_heads, dk, dv, page_size, ctypes.c_float(scale), ctypes.c_float(softcap), _ptr(sink), mask,
+        mask_size, dtype_code(q.dtype), _stream()), "scored_decode", 2)
+
+
+# -- learned routers ----------------------------------------------------------------------------------------
+def moe_route_top(logits: torch.Tensor, n_experts: int, top: int):
+    """The ``top`` largest of each row's first ``n_experts`` logits (float32, rows may be wider), weighted by the
+    softmax over the chosen logits only; among equal logits the lower expert wins. Returns (expert_of int32
+    [tokens * top], weight_of float32 [tokens * top]) in order of falling logit."""
+    _need(logits, "logits", torch.float32, contiguous=False)
+    n = logits.size(0)
+    if logits.size(1) < n_experts or not 1 <= top <= n_experts:
+        raise KernelError(f"moe_route_top: logits {tuple(logits.shape)}, {n_experts} experts, top {top}")
+    expert_of = torch.empty((n * top,), dtype=torch.int32, device=logits.device)
+    weight_of = torch.empty((n * top,), dtype=torch.float32, device=logits.device)
+    _check(_lib().llmrs_moe_route_top(_ptr(logits), _LL(_row_stride(logits, "logits")), _ptr(expert_of),
+                                      _ptr(weight_of), n, n_experts, top, _stream()), "moe_route_top")
+    return expert_of, weight_of
+
+
+def moe_combine_shared(rows, row_of, weight_of, top: int, shared: Optional[torch.Tensor] = None,
+                       shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``moe_combine`` plus an expert that every token uses: ``out[t] += sigmoid(shared_gate[t]) * shared[t]``
+    (``shared_gate``: float32, one number per token, any stride; None: the shared rows are added as they are)."""
+    _need(rows, "rows", torch.float32)
+    n = row_of.numel() // top
+    out = torch.empty((n, rows.size(1)), dtype=torch.float32, device=rows.device)
+    if shared is not None:
+        _need(shared, "shared")
+        if shared.shape != out.shape:
+            raise KernelError(f"moe_combine_shared: shared {tuple(shared.shape)}, out {tuple(out.shape)}")
+    gate_stride = 0
+    if shared_gate is not None:
+        _need(shared_gate, "shared_gate", torch.float32, contiguous=False)
+        gate_stride = shared_gate.stride(0)
+    _check(_lib().llmrs_moe_combine_shared(
+        _ptr(rows), _ptr(row_of), _ptr(weight_of), _ptr(shared), dtype_code(shared.dtype) if shared is not None else F32,
+        _ptr(shared_gate), _LL(gate_stride), _ptr(out), n, top, rows.size(1), _stream()), "moe_combine_shared")
+    return out

@@ -139,3 +139,61 @@ class OutNormBlock(Block):
                 h, None, None, ctx, self.act_dtype)
             self.feed_forward_norm.add_normed(h, self.feed_forward.forward(x, ctx))
         return h, None
+
+
+@register("block", "postnorm")
+class PostNormBlock(Block):
+    """``h = norm1(alpha * h + ls1 * mixer(h)); h = norm2(alpha * h + ls2 * feed_forward(h))``: the norm comes after
+    the residual sum, the branches read the stream itself (rounded to the activation type by the norm's own pass) and
+    each branch's output may be scaled channel by channel before the sum (layer scale). ``alpha`` weighs the stream in
+    the sum. ``layer_scale`` names the two scale vectors after the layer's prefix ((), or ("", "") : none); a layer
+    may have no feed-forward, and then no second norm unless ``lone_norm`` keeps it (``h = norm2(alpha * h)``).
+    Sums, statistics and the normed stream are float32."""
+
+    def __init__(self, layer: LayerSpec, alpha: float = 1.0, layer_scale=(), lone_norm: bool = False, prefix: str = ""):
+        p = layer.prefix
+        self.alpha = float(alpha)
+        self.mixer_norm = build("norm", layer.mixer_norm, prefix=p)
+        self.mixer = build("mixer", layer.mixer, prefix=p + layer.mixer_scope)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward = build("feed_forward", layer.feed_forward, prefix=p + layer.feed_forward_scope)
+        if layer.feed_forward is not None or lone_norm:
+            self.feed_forward_norm = build("norm", layer.feed_forward_norm, prefix=p)
+        names = tuple(layer_scale) + ("", "")
+        self.scale_names = [p + n if n else "" for n in names[:2]]
+        if self.feed_forward is None:
+            self.scale_names[1] = ""
+        self.dim = self.mixer_norm.dim
+        self.scales = [None, None]
+
+    def parts(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm) if p is not None]
+
+    def chain(self):
+        return []
+
+    def weight_specs(self):
+        specs = [s for part in self.parts() for s in part.weight_specs()]
+        return specs + [WeightSpec(n, (self.dim,), role="norm") for n in self.scale_names if n]
+
+    def bind(self, tensors, runtime: Runtime):
+        self.act_dtype = runtime.act_dtype
+        for part in self.parts():
+            part.bind(tensors, runtime)
+        self.scales = [tensors[n].to(torch.float32).contiguous() if n else None for n in self.scale_names]
+
+    def forward(self, h, pending, ctx, cache):
+        if pending is not None:      # a block of another kind left its last branch unadded
+            ops.residual_add(h, pending)
+            ctx.stream_copy = None
+        # The norm that ends a block leaves the stream's rounded copy for the block after it (same step, same stream).
+        left = getattr(ctx, "stream_copy", None)
+        x = left[1] if left is not None and left[0] is h else ops.token_shift(h, None, None, ctx, self.act_dtype)
+        y = self.mixer.forward(x, ctx, cache)
+        x = self.mixer_norm.post_normed(h, y, self.scales[0], self.alpha, self.act_dtype)
+        if self.feed_forward_norm is not None:
+            y = self.feed_forward.forward(x, ctx) if self.feed_forward is not None else None
+            x = self.feed_forward_norm.post_normed(h, y, self.scales[1], self.alpha, self.act_dtype)
+        ctx.stream_copy = (h, x)
+        return h, None

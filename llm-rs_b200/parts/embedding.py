@@ -34,11 +34,13 @@ class LinearHead(Part):
     (llm-core/src/graph/builder.rs:408-437). ``tied_to`` names the embedding table that
     serves as W when the model ties them (llm-core/src/backends/weights.rs:144-157): one
     buffer, used by both. A tied model's folder may still store the head's matrix (a copy of the
-    table); it is accepted and not read. ``softcap`` > 0: ``logits = softcap * tanh(logits / softcap)``."""
+    table); it is accepted and not read. ``scale`` other than 1 multiplies the float32 logits; ``softcap`` > 0:
+    ``logits = softcap * tanh(logits / softcap)`` (after the scale)."""
 
     def __init__(self, vocab_size: int, hidden_size: int, name: str = "head.weight", tied_to: str = "",
-                 softcap: float = 0.0, prefix: str = ""):
+                 softcap: float = 0.0, scale: float = 1.0, prefix: str = ""):
         self.vocab_size, self.hidden_size, self.softcap = vocab_size, hidden_size, float(softcap)
+        self.scale = float(scale)
         self.name, self.tied_to = prefix + name, tied_to
 
     def weight_specs(self):
@@ -54,4 +56,6 @@ class LinearHead(Part):
 
     def forward(self, x):
         logits = self.proj.forward(x, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            ops.scale_(logits, self.scale)
         return ops.softcap_(logits, self.softcap) if self.softcap > 0 else logits

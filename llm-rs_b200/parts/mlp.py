@@ -86,3 +86,36 @@ class SwiGLU(FeedForward):
         if residual is not None:
             return self.down.forward_into_residual(act, residual)
         return self.down.forward(act)
+
+
+@register("feed_forward", "dense")
+class DenseFF(FeedForward):
+    """``down(act(up(x)))`` without a gate; ``activation`` "relu_sq" is the square of relu. ``names`` maps the roles
+    up and down to the tensors' names after the prefix."""
+    ROLES = ("up", "down")
+    ACTIVATIONS = ("relu_sq",)
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu_sq", names=None,
+                 prefix: str = ""):
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {self.ACTIVATIONS}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.prefix = prefix
+        self.names = {role: role for role in self.ROLES}
+        self.names.update(names or {})
+        if set(self.names) != set(self.ROLES):
+            raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
+
+    def weight_specs(self):
+        H, I = self.hidden_size, self.intermediate_size
+        return [WeightSpec(self.prefix + self.names["up"], (I, H)), WeightSpec(self.prefix + self.names["down"], (H, I))]
+
+    def bind(self, tensors, runtime: Runtime):
+        self.up = Linear(tensors[self.prefix + self.names["up"]], None, runtime.act_dtype)
+        self.down = Linear(tensors[self.prefix + self.names["down"]], None, runtime.act_dtype)
+
+    def chain(self):
+        return [self.up, self.down]
+
+    def forward(self, x, ctx):
+        return self.down.forward(ops.relu_sq(self.up.forward(x)))

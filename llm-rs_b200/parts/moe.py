@@ -1,6 +1,8 @@
 """Mixtures of experts."""
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .. import ops
@@ -19,8 +21,16 @@ class MixtureOfExperts(FeedForward):
     parameters.
 
     Router ``"table"``: no learned router; an integer table [vocab, top] names each token id's experts (the entries
-    of a row differ), each weighted 1/top. The router only fills (expert, weight) per assignment on the device; the
+    of a row differ), each weighted 1/top. Router ``"linear"``: logits ``W_router x + b`` as a float32 product (x may be
+    its rounding to the activation type), the ``top`` largest are chosen (the lower expert among equals) and weighted
+    by the softmax over the chosen logits only. A router only fills (expert, weight) per assignment on the device; the
     grouping of rows by expert, the two grouped products and the weighted sum do not depend on which router ran.
+
+    ``limit`` None leaves gate and up unclamped; with ``alpha`` 1 and ``up_shift`` 0 the unit is ``silu(g) * u``.
+
+    ``shared_size`` > 0 adds an expert of that size and the same form that every token uses (one fused gate|up
+    product, as the dense gated feed-forward); with ``shared_gated`` its output is multiplied by
+    ``sigmoid(w_sg . x)``, one number per token, computed beside the router's logits.
 
     The rows are sorted by expert so that a tile of rows shares one expert's weights; the first product has the gated
     unit as its epilogue; bfloat16 products run on the tensor cores (``csrc/gemm_grouped.cu``). ``forward`` takes the
@@ -28,22 +38,25 @@ class MixtureOfExperts(FeedForward):
     ``<prefix>table`` unless ``names`` renames the roles."""
 
     reads_residual = True
-    ROLES = ("expert", "gate", "up", "down", "table")
+    ROLES = ("expert", "gate", "up", "down", "table", "router", "router_bias", "shared", "shared_gate")
 
     def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top: int, vocab_size: int = 0,
-                 router: str = "table", limit: float = 1.0, alpha: float = 1.702, up_shift: float = 1.0,
-                 names=None, prefix: str = ""):
-        if router != "table":
-            raise ValueError(f"unknown router {router!r}; known: 'table'")
+                 router: str = "table", limit: Optional[float] = 1.0, alpha: float = 1.702, up_shift: float = 1.0,
+                 shared_size: int = 0, shared_gated: bool = False, names=None, prefix: str = ""):
+        if router not in ("table", "linear"):
+            raise ValueError(f"unknown router {router!r}; known: 'table', 'linear'")
         if not 1 <= top <= n_experts:
             raise ValueError(f"top {top} of {n_experts} experts")
         if router == "table" and vocab_size < 1:
             raise ValueError("the table router needs the vocabulary's size")
         self.hidden_size, self.expert_size, self.n_experts, self.top = hidden_size, expert_size, n_experts, top
         self.vocab_size, self.router = vocab_size, router
-        self.limit, self.alpha, self.up_shift = float(limit), float(alpha), float(up_shift)
+        self.limit = float("inf") if limit is None else float(limit)
+        self.alpha, self.up_shift = float(alpha), float(up_shift)
+        self.shared_size, self.shared_gated = int(shared_size), bool(shared_gated) and shared_size > 0
         self.prefix = prefix
-        self.names = {"expert": "e{}.", "gate": "gate", "up": "up", "down": "down", "table": "table"}
+        self.names = {"expert": "e{}.", "gate": "gate", "up": "up", "down": "down", "table": "table",
+                      "router": "router", "router_bias": "router.b", "shared": "shared.", "shared_gate": "shared.sg"}
         self.names.update(names or {})
         if set(self.names) != set(self.ROLES):
             raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
@@ -57,8 +70,18 @@ class MixtureOfExperts(FeedForward):
         for e in range(self.n_experts):
             specs += [WeightSpec(self._name(e, "gate"), (F, H)), WeightSpec(self._name(e, "up"), (F, H)),
                       WeightSpec(self._name(e, "down"), (H, F))]
-        specs.append(WeightSpec(self.prefix + self.names["table"], (self.vocab_size, self.top), role="expert_table",
-                                limit=self.n_experts))
+        if self.router == "table":
+            specs.append(WeightSpec(self.prefix + self.names["table"], (self.vocab_size, self.top),
+                                    role="expert_table", limit=self.n_experts))
+        else:
+            specs += [WeightSpec(self.prefix + self.names["router"], (self.n_experts, H)),
+                      WeightSpec(self.prefix + self.names["router_bias"], (self.n_experts,), role="bias")]
+        if self.shared_size:
+            S, sp = self.shared_size, self.prefix + self.names["shared"]
+            specs += [WeightSpec(sp + self.names["gate"], (S, H)), WeightSpec(sp + self.names["up"], (S, H)),
+                      WeightSpec(sp + self.names["down"], (H, S))]
+            if self.shared_gated:
+                specs.append(WeightSpec(self.prefix + self.names["shared_gate"], (1, H)))
         return specs
 
     def bind(self, tensors, runtime: Runtime):
@@ -67,22 +90,45 @@ class MixtureOfExperts(FeedForward):
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
         if len({self.w_gate.dtype, self.w_up.dtype, self.w_down.dtype}) != 1:
             self.w_gate, self.w_up, self.w_down = (w.to(torch.float32) for w in (self.w_gate, self.w_up, self.w_down))
-        self.table = tensors[self.prefix + self.names["table"]].contiguous()
-        bad = (self.table < 0) | (self.table >= self.n_experts)
-        if bool(bad.any()):
-            raise ValueError(f"{self.prefix}{self.names['table']} names experts outside 0..{self.n_experts - 1}")
+        self.table = self.router_w = self.router_b = self.shared = None
+        if self.router == "table":
+            self.table = tensors[self.prefix + self.names["table"]].contiguous()
+            bad = (self.table < 0) | (self.table >= self.n_experts)
+            if bool(bad.any()):
+                raise ValueError(f"{self.prefix}{self.names['table']} names experts outside 0..{self.n_experts - 1}")
+        rows, bias = [], []
+        if self.router == "linear":
+            rows.append(tensors[self.prefix + self.names["router"]].to(torch.float32))
+            bias.append(tensors[self.prefix + self.names["router_bias"]].to(torch.float32))
+        if self.shared_gated:       # the shared expert's gate is one more row of the router's product
+            rows.append(tensors[self.prefix + self.names["shared_gate"]].to(torch.float32))
+            bias.append(torch.zeros((1,), dtype=torch.float32, device=rows[-1].device))
+        if rows:
+            self.router_w, self.router_b = torch.cat(rows, dim=0).contiguous(), torch.cat(bias, dim=0).contiguous()
+        if self.shared_size:
+            from .mlp import SwiGLU
+            sp = self.prefix + self.names["shared"]
+            self.shared = SwiGLU(self.hidden_size, self.shared_size)
+            self.shared.bind({self.shared._name(r): tensors[sp + self.names[r]] for r in ("gate", "up", "down")}, runtime)
 
     def forward(self, x, ctx):
         """x: the step's rows, float32 (the residual stream) or the activation type. Returns float32 [tokens, hidden]."""
-        expert_of, weight_of = ops.moe_route_table(ctx.token_ids, self.table, self.n_experts)
+        if self.act_dtype == torch.bfloat16 and x.dtype == torch.float32:
+            x = ops.token_shift(x, None, None, None, torch.bfloat16)     # the rows as activations: the tensor cores' type
+        logits = ops.gemm_f32(x, self.router_w, self.router_b) if self.router_w is not None else None
+        if self.router == "table":
+            expert_of, weight_of = ops.moe_route_table(ctx.token_ids, self.table, self.n_experts)
+        else:
+            expert_of, weight_of = ops.moe_route_top(logits, self.n_experts, self.top)
         n_rows = expert_of.numel()
         tile_rows = ops.grouped_tile_rows(n_rows, self.n_experts)
         row_of, src_token, tiles, n_tiles = ops.moe_sort(expert_of, self.top, self.n_experts, tile_rows)
-        if self.act_dtype == torch.bfloat16 and x.dtype == torch.float32:
-            x = ops.token_shift(x, None, None, None, torch.bfloat16)     # the rows as activations: the tensor cores' type
         act = torch.empty((n_rows, self.expert_size), dtype=self.act_dtype, device=x.device)
         ops.gemm_grouped(x, self.w_gate, act, tiles, n_tiles, src_token, w2=self.w_up, limit=self.limit,
                          alpha=self.alpha, shift=self.up_shift, tile_rows=tile_rows)
         rows = torch.empty((n_rows, self.hidden_size), dtype=torch.float32, device=x.device)
         ops.gemm_grouped(act, self.w_down, rows, tiles, n_tiles, None, tile_rows=tile_rows)
-        return ops.moe_combine(rows, row_of, weight_of, self.top)
+        if self.shared is None:
+            return ops.moe_combine(rows, row_of, weight_of, self.top)
+        gate = logits[:, logits.size(1) - 1] if self.shared_gated else None
+        return ops.moe_combine_shared(rows, row_of, weight_of, self.top, self.shared.forward(x, ctx), gate)

@@ -18,7 +18,8 @@ class RMSNorm(Norm):
     ``name`` is the weight's name after the prefix. With ``offset`` the stored weight lies around zero and the
     factor is ``offset + w`` (added once at load, in float32).
 
-    ``add_normed(h, y)`` is the norm of a block that norms a branch's OUTPUT: ``h += norm(y)``."""
+    ``add_normed(h, y)`` is the norm of a block that norms a branch's OUTPUT: ``h += norm(y)``;
+    ``post_normed(h, y, ...)`` that of a block that norms after the residual sum."""
 
     def __init__(self, dim: int, eps: float, name: str = "weight", offset: float = 0.0, prefix: str = ""):
         self.dim, self.eps, self.prefix, self.name = dim, float(eps), prefix, name
@@ -40,6 +41,11 @@ class RMSNorm(Norm):
 
     def add_normed(self, h, y):
         return ops.outnorm_add(h, y, self.weight, self.eps)
+
+    def post_normed(self, h, y, layer_scale, alpha: float, out_dtype=None):
+        """The norm of a block that norms AFTER the sum: ``h = norm(alpha * h + y * layer_scale)`` in place; returns
+        the rows rounded to ``out_dtype`` (what the next branch reads), or None without one."""
+        return ops.post_norm(h, y, layer_scale, self.weight, alpha, self.eps, out_dtype)
 
     def link(self):
         return (self.weight, self.eps) if self.act_dtype == torch.bfloat16 else None

@@ -1,0 +1,148 @@
+"""Grouped-query attention whose scores are capped, whose softmax has a sink, and whose mask may be chunked."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import host, ops
+from .attention import PREFILL_TILE
+from .base import Mixer, Plan, Runtime, StepInfo
+from .linear import Linear
+from .registry import register
+from .spec import CacheNeed, WeightSpec
+
+MASKS = {"causal": ops.MASK_CAUSAL, "window": ops.MASK_WINDOW, "chunk": ops.MASK_CHUNK}
+DECODE_SPLIT_KEYS = 256     # keys per block of the decode kernel
+
+
+@register("mixer", "scored_attention")
+class ScoredAttention(Mixer):
+    """``n_heads`` query heads over ``n_kv_heads`` key/value heads (query head h reads key head h // (n_heads /
+    n_kv_heads)); keys of ``dim`` channels, values of ``vdim``. In order:
+
+    q, k, v projections (no biases) -> RMS norm over the WHOLE q row and the whole k row, all heads at once, with
+    plain weights of that size (``qk_norm`` "whole"; "none": no norm) -> rotation of the first ``rot_dims`` channels
+    of every head, channel i paired with i + rot_dims/2, angle position * rot_base^(-2i/rot_dims) (q and k, not v)
+    -> new keys and values into the pages -> score = (q . k) * ``scale``, then ``softcap * tanh(score / softcap)``
+    when ``softcap`` > 0 -> mask: causal, and with ``mask`` "window" the last ``mask_size`` keys, with "chunk" only
+    keys of the query's own chunk of ``mask_size`` positions (chunks counted from position 0 of the sequence) ->
+    softmax whose denominator also holds exp(sink_h), one learned number per query head (``sink``; it has no key
+    and no value and is neither scaled nor capped) -> output projection.
+
+    Scores, weights, norms, positions and angles are float32 (angles are made in double). Pages: a group of kind
+    "window" for the masks that bound how far back a query reads (a chunk never reaches further back than
+    ``mask_size`` - 1 keys), else "full"; a token stores ``dim`` + ``vdim`` numbers per key head. Prompt portions run
+    on the tensor cores in bfloat16 (``csrc/attention_scored.cu``); requests that bring one token take the decode
+    kernel in the same step. ``names`` maps the roles q, k, v, o, q_norm, k_norm, sink."""
+    ROLES = ("q", "k", "v", "o", "q_norm", "k_norm", "sink")
+
+    def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
+                 softcap: float = 0.0, sink: bool = False, mask: str = "causal", mask_size: int = 0,
+                 qk_norm: str = "whole", norm_eps: float = 1e-6, rot_dims: int = 0, rot_base: float = 10000.0,
+                 names=None, prefix: str = ""):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} key/value heads")
+        if mask not in MASKS or (mask != "causal" and mask_size < 1):
+            raise ValueError(f"mask {mask!r} of size {mask_size}; known masks: {sorted(MASKS)}")
+        if qk_norm not in ("whole", "none"):
+            raise ValueError(f"unknown qk_norm {qk_norm!r}; known: 'whole', 'none'")
+        if rot_dims % 2 or not 0 <= rot_dims <= dim:
+            raise ValueError(f"rot_dims {rot_dims} must be even and at most dim {dim}")
+        if not (1 <= dim <= 256 and 1 <= vdim <= 256):
+            raise ValueError(f"head sizes {dim} / {vdim}: the attention kernels take 1 to 256")
+        self.hidden_size, self.n_heads, self.n_kv_heads, self.dim, self.vdim = hidden_size, n_heads, n_kv_heads, dim, vdim
+        self.scale, self.softcap, self.has_sink = float(scale), float(softcap), bool(sink)
+        self.mask, self.mask_size = mask, int(mask_size) if mask != "causal" else 0
+        self.qk_norm, self.norm_eps = qk_norm, float(norm_eps)
+        self.rot_dims, self.rot_base = int(rot_dims), float(rot_base)
+        self.prefix = prefix
+        self.names = {"q": "q", "k": "k", "v": "v", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm", "sink": "sink"}
+        self.names.update(names or {})
+        if set(self.names) != set(self.ROLES):
+            raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
+        self.q_width, self.k_width, self.v_width = n_heads * dim, n_kv_heads * dim, n_kv_heads * vdim
+
+    def _name(self, role: str) -> str:
+        return self.prefix + self.names[role]
+
+    def weight_specs(self):
+        H, nm = self.hidden_size, self._name
+        specs = [WeightSpec(nm("q"), (self.q_width, H)), WeightSpec(nm("k"), (self.k_width, H)),
+                 WeightSpec(nm("v"), (self.v_width, H)), WeightSpec(nm("o"), (H, self.n_heads * self.vdim))]
+        if self.qk_norm == "whole":
+            specs += [WeightSpec(nm("q_norm"), (self.q_width,), role="norm"),
+                      WeightSpec(nm("k_norm"), (self.k_width,), role="norm")]
+        if self.has_sink:
+            specs.append(WeightSpec(nm("sink"), (self.n_heads,), role="bias"))
+        return specs
+
+    def bind(self, tensors, runtime: Runtime):
+        nm = self._name
+        self.act_dtype = runtime.act_dtype
+        ws = [tensors[nm(r)] for r in "qkv"]
+        dt = ws[0].dtype if all(w.dtype == ws[0].dtype for w in ws) else torch.float32
+        wqkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
+        self.qkv_proj = Linear(wqkv, None, runtime.act_dtype)
+        self.q_proj = Linear(wqkv[: self.q_width], None, runtime.act_dtype)     # for entries that read another's pages
+        self.o_proj = Linear(tensors[nm("o")], None, runtime.act_dtype)
+        f32 = lambda role: tensors[nm(role)].to(torch.float32).contiguous()
+        self.q_norm_w = f32("q_norm") if self.qk_norm == "whole" else None
+        self.k_norm_w = f32("k_norm") if self.qk_norm == "whole" else None
+        self.sink = f32("sink") if self.has_sink else None
+        i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+        self.inv_freq = (self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))).to(runtime.device)
+
+    def cache_need(self):
+        kind = "full" if self.mask == "causal" else "window"
+        return CacheNeed(kind, self.n_kv_heads, self.dim, self.mask_size, planes=(self.dim, self.vdim))
+
+    # The plan of paged attention (tiles of prompt portions, the list of single tokens) is the one grouped-query
+    # attention makes: layers of either kind share it within a step.
+    def plan_key(self):
+        return ("paged_attention", PREFILL_TILE)
+
+    def plan(self, step: StepInfo) -> Plan:
+        tiles, decode, max_kv, long_portions = host.plan_paged_attention(step.n_new, step.cached_len, PREFILL_TILE)
+        if step.for_graph and decode.size and step.block_tables:
+            max_kv = max(t.shape[1] for t in step.block_tables) * step.page_size
+        return Plan(arrays={"prefill_tiles": tiles, "decode_reqs": decode},
+                    values={"n_prefill_tiles": int(tiles.shape[0]), "n_decode": int(decode.size),
+                            "max_decode_kv_len": int(max_kv), "long_portions": int(long_portions)})
+
+    def forward(self, x, ctx, cache):
+        table = cache.block_table
+        if cache.owns:
+            qkv = self.qkv_proj.forward(x)
+            q = qkv[:, : self.q_width]
+            k = qkv[:, self.q_width: self.q_width + self.k_width]
+            v = qkv[:, self.q_width + self.k_width:]
+        else:
+            q, k, v = self.q_proj.forward(x), None, None
+        pages = _pages(cache)
+        ops.scored_prepare(q, k, v, self.q_norm_w, self.k_norm_w, self.inv_freq, ctx, table,
+                           pages if cache.owns else None, self.n_heads, self.n_kv_heads, self.dim, self.vdim,
+                           self.rot_dims, cache.page_size, self.norm_eps)
+        out = torch.empty((ctx.n_tokens, self.n_heads * self.vdim), dtype=q.dtype, device=q.device)
+        plan = ctx.plan(self.plan_key())
+        n_tiles, n_decode, max_kv = (plan.values[key] for key in ("n_prefill_tiles", "n_decode", "max_decode_kv_len"))
+        mask = MASKS[self.mask]
+        args = (self.n_heads, self.n_kv_heads, self.dim, self.vdim, cache.page_size, self.scale, self.softcap,
+                self.sink, mask, self.mask_size)
+        if n_tiles:
+            ops.scored_prefill(q, out, pages, plan.arrays["prefill_tiles"], n_tiles, ctx, table, *args)
+        if n_decode:
+            span = max(1, min(max_kv, self.mask_size) if self.mask_size else max_kv)   # keys a query can see at most
+            splits = -(-span // DECODE_SPLIT_KEYS)
+            ops.scored_decode(q, out, pages, plan.arrays["decode_reqs"], n_decode, ctx, table, splits,
+                              DECODE_SPLIT_KEYS, *args)
+        return self.o_proj.forward(out)
+
+
+def _pages(cache) -> torch.Tensor:
+    """One entry's pages as the kernels address them: [pages, key heads, page_size * (dim + vdim)]. The planes are
+    views into that tensor; the first one starts where it starts."""
+    keys, values = cache.planes
+    n_pages, n_heads, page_size, dk = keys.shape
+    return keys.as_strided((n_pages, n_heads, page_size * (dk + values.size(3))),
+                           (keys.stride(0), keys.stride(1), 1), keys.storage_offset())
