@@ -163,3 +163,25 @@ def forward(config: dict, w: Dict[str, torch.Tensor], tokens: List[int], layers_
             layers_out.append(x.clone())
     x = rms(x, eps) * w["final.norm"]
     return (x @ w["head"].T) * float(config["logit_scale"])
+
+
+# -- folders and generation -----------------------------------------------------------------------------
+def load_model_dir(path: str):
+    """(config dict, {name: float64 tensor}) of a model folder."""
+    import json
+    import os
+
+    from plain_rusadra import read_safetensors
+    with open(os.path.join(path, "config.json")) as f:
+        cfg = json.load(f)
+    w = read_safetensors(os.path.join(path, "model.safetensors"))
+    return cfg, {k: v.to(F64) for k, v in w.items()}
+
+
+def greedy_generate(config: dict, w, prompt: List[int], n_new: int) -> List[int]:
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        t = int(forward(config, w, toks)[-1].argmax())
+        out.append(t)
+        toks.append(t)
+    return out
