@@ -19,8 +19,8 @@ A "step" is one decode step of the whole batch. The default is batch 8 at a cont
 
 The K timed steps run back to back as five runs of K/5 steps with a CUDA event between them: ``value`` and
 ``ms_per_step`` are the median run's, ``repeats`` gives the runs' spread and the mean over all K steps.
-``--workload rusadra`` measures the Rusadra design beside Qwen3 at equal size instead (see DESIGN_SIZES below); the
-default workload and its JSON line are unchanged by it.
+``--workload rusadra`` measures the Rusadra design beside Qwen3 at equal size instead (see DESIGN_SIZES below), and
+``--workload pusazen`` the Pusazen design beside Rusadra; the default workload and its JSON line are unchanged by them.
 Fractions are given against two denominators: the peaks measured on this pool (MEASURED_PEAKS.json beside
 this file when present, else 6.65 TB/s and 1.59 PFLOP/s) and the nominal figures of the part (7.7 TB/s,
 2.25 PFLOP/s dense bf16). Only N = 1 is supported: the engine is a single-GPU engine.
@@ -84,7 +84,31 @@ def design_configs(z):
     return rus, qwen
 
 
-def run_design(args):
+# ``--workload pusazen``: the Pusazen design (matrix-memory, chunked-attention and lightning layers in turn, norms after
+# the residual sums, a learned router with a shared expert) beside the Rusadra design, its closest relative in this
+# package (a recurrent mixer with a matrix state, windowed attention, routed experts), at equal width, depth,
+# vocabulary, experts and expert width; the same measurements as ``--workload rusadra``.
+def pusazen_configs(z):
+    """(Pusazen config.json, Rusadra config.json) of one entry of DESIGN_SIZES."""
+    memory = {"type": "mlstm", "mixer": {"heads": z["delta_heads"] // 2, "dim": 2 * z["delta_dim"],
+                                         "vdim": 2 * z["delta_dim"], "gate_cap": 15.0}}
+    lightning = {"type": "lightning", "mixer": {
+        "heads": z["delta_heads"] // 2, "dim": 2 * z["delta_dim"], "vdim": 2 * z["delta_dim"],
+        "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, z["delta_heads"] // 2 - 1)) for h in range(z["delta_heads"] // 2)]}}
+    attention = {"type": "attention", "mixer": {
+        "heads": z["heads"], "kv_heads": max(1, z["heads"] // 4), "dim": z["dim"], "vdim": z["vdim"],
+        "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["window"]}, "rot": {"base": 1e6, "dims": z["rot"]}}}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["ff"]}}
+    order = (memory, attention, lightning, attention)
+    pus = {"architecture": "Pusazen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+           "postln_alpha": 2.0, "logit_scale": 0.5,
+           "layers": [dict(order[i % 4], mlp=mlp) for i in range(z["layers"])]}
+    return pus, design_configs(z)[0]
+
+
+def run_design(args, configs=None, workload="rusadra"):
+    configs = configs or design_configs
     import numpy as np
     import torch
     import llm_rs_b200  # noqa: F401
@@ -104,7 +128,7 @@ def run_design(args):
     sampler.start()
     out = {}
     for size, z in DESIGN_SIZES.items():
-        for raw in design_configs(z):
+        for raw in configs(z):
             entry = resolve_architecture(raw)
             spec = entry.build_spec(entry.config_cls.from_dict(raw))
             name = f"{entry.name} {size}"
@@ -145,8 +169,9 @@ def run_design(args):
                 for rid in ids:      # cached context without a prefill: the step reads the same bytes whatever they hold
                     rec = runner.manager.admit(rid)
                     runner.storage.reset_slot(rec.slot)
-                    runner.manager.reserve(rid, ctx_len - W - K)
-                    runner.manager.commit(rid, ctx_len - W - K)
+                    # (one less than the steps need: the profiled step after them then ends the context, not starts the next)
+                    runner.manager.reserve(rid, ctx_len - W - K - 1)
+                    runner.manager.commit(rid, ctx_len - W - K - 1)
                 toks = rng.integers(0, V, (W + K, batch)).tolist()
                 for s in range(W):
                     runner.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
@@ -176,7 +201,7 @@ def run_design(args):
             del runner
             torch.cuda.empty_cache()
     clocks = sampler.stop()
-    print(json.dumps({"workload": "rusadra", "dtype": "bf16", "data": "synthetic: random weights, random token ids",
+    print(json.dumps({"workload": workload, "dtype": "bf16", "data": "synthetic: random weights, random token ids",
                       "peaks": pk, "sizes": DESIGN_SIZES, "results": out, "launches": ops.launch_count, "clocks": clocks}))
     return 0
 
@@ -373,11 +398,12 @@ def main():
     ap.add_argument("--profile", action="store_true", help="instead of the benchmark: time every kernel class of one "
                     "decode step and of the prefill with CUDA events (eager launches, NVTX ranges) and print a table "
                     "with bytes, flops and the fraction of the peaks to standard error, the rows as JSON to standard output")
-    ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS, "rusadra"],
+    ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS, "rusadra", "pusazen"],
                     help="decode: the benchmark contract (default). mixed14b / stress32b: a whole serving run "
                     "through the engine on the layer sizes of Qwen3-14B / Qwen3-32B. rusadra: prefill and decode of the "
                     "Rusadra design beside Qwen3 at equal width, depth, vocabulary and active feed-forward width, with "
-                    "every kernel class's fraction of the device's peaks")
+                    "every kernel class's fraction of the device's peaks. pusazen: the same for the Pusazen design "
+                    "beside Rusadra at equal width, depth, vocabulary, experts and expert width")
     ap.add_argument("--pool-tokens", type=int, default=0, help="size of the cache pool of a --workload run in "
                     "tokens (default: what holds every request whole); smaller makes the scheduler preempt")
     args = ap.parse_args()
@@ -390,6 +416,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload == "pusazen":
+        return run_design(args, pusazen_configs, "pusazen")
     if args.workload == "rusadra":
         return run_design(args)
     if args.workload != "decode":

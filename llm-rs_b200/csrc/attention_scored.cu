@@ -533,11 +533,12 @@ LLMRS_API int llmrs_scored_prefill(const void* q, long long q_stride, void* out,
 // decode
 // ---------------------------------------------------------------------------------
 constexpr int SD_WARPS = 4, SD_THREADS = SD_WARPS * 32, SD_MAXC = 8;      // channels per lane: head sizes up to 256
+constexpr int SD_UNROLL = 4;                                               // keys a warp takes per turn
 
 __host__ __device__ inline size_t sd_part_stride(int dv) { return (size_t)dv + 2; }
 
-// One block per (decode request, query head, run of keys). Each warp takes every fourth key of the run: its lanes
-// split the channels, the dot product is summed over the warp, the weights and the sum of values are kept online.
+// One block per (decode request, query head, run of keys). Each warp takes four keys of every sixteen of the run: its
+// lanes split the channels, the dot products are summed over the warp, the weights and the sum of values are kept online.
 template <typename T>
 __global__ void __launch_bounds__(SD_THREADS)
 scored_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ cache,
@@ -568,22 +569,48 @@ scored_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __res
     acc[j] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
-  for (int key = k_begin + warp; key < k_end; key += SD_WARPS) {
-    const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 3, key);
-    const T* kr = cache + page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)(key % page_size) * dk;
-    const T* vr = cache + page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk +
-                  (size_t)(key % page_size) * dv;
-    float dot = 0.f;
+  // Four keys per turn: their rows are all asked for before the first is used, so that a warp has several loads on
+  // their way (one key at a time, the kernel waited a memory round trip per key).
+  for (int key0 = k_begin + warp * SD_UNROLL; key0 < k_end; key0 += SD_WARPS * SD_UNROLL) {
+    float kf[SD_UNROLL][SD_MAXC], vf[SD_UNROLL][SD_MAXC];
 #pragma unroll
-    for (int j = 0; j < SD_MAXC; ++j)
-      if (lane + 32 * j < dk) dot = fmaf(qr[j], to_float(kr[lane + 32 * j]), dot);
-    const float s = capped(opt, warp_sum(dot));
-    const float m_new = fmaxf(m, s), corr = expf(m - m_new), p = expf(s - m_new);
-    l = l * corr + p;
+    for (int u = 0; u < SD_UNROLL; ++u) {
+      const int key = min(key0 + u, k_end - 1);
+      const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 3, key);
+      const T* kr = cache + page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)(key % page_size) * dk;
+      const T* vr = cache + page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk +
+                    (size_t)(key % page_size) * dv;
+#pragma unroll
+      for (int j = 0; j < SD_MAXC; ++j) {
+        kf[u][j] = lane + 32 * j < dk ? to_float(kr[lane + 32 * j]) : 0.f;
+        vf[u][j] = lane + 32 * j < dv ? to_float(vr[lane + 32 * j]) : 0.f;
+      }
+    }
+    float sc[SD_UNROLL], m_new = m;
+#pragma unroll
+    for (int u = 0; u < SD_UNROLL; ++u) {
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < SD_MAXC; ++j) dot = fmaf(qr[j], kf[u][j], dot);
+      sc[u] = key0 + u < k_end ? capped(opt, warp_sum(dot)) : -INFINITY;      // the first of the four always counts
+      m_new = fmaxf(m_new, sc[u]);
+    }
+    const float corr = expf(m - m_new);
+    float p[SD_UNROLL], ps = 0.f;
+#pragma unroll
+    for (int u = 0; u < SD_UNROLL; ++u) {
+      p[u] = expf(sc[u] - m_new);
+      ps += p[u];
+    }
+    l = l * corr + ps;
     m = m_new;
 #pragma unroll
-    for (int j = 0; j < SD_MAXC; ++j)
-      if (lane + 32 * j < dv) acc[j] = fmaf(p, to_float(vr[lane + 32 * j]), acc[j] * corr);
+    for (int j = 0; j < SD_MAXC; ++j) {
+      float a = acc[j] * corr;
+#pragma unroll
+      for (int u = 0; u < SD_UNROLL; ++u) a = fmaf(p[u], vf[u][j], a);
+      acc[j] = a;
+    }
   }
   if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
 #pragma unroll

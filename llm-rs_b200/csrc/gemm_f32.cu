@@ -84,3 +84,109 @@ LLMRS_API int llmrs_gemm_f32_bf16_rows(const void* x, long long x_stride, const 
                                                                   x_stride, out_stride);
   return llmrs_launch_status("gemm_f32 (bfloat16 rows)");
 }
+
+// ---------------------------------------------------------------------------------
+// Few output features (a router's logits, the gates of a recurrence, a single gate row): out[m, n] for n < N <= some
+// hundreds. The tiled kernel above would run as one or two blocks that walk K alone; here a block holds SK_TOKENS
+// rows of x in shared memory and each of its warps owns one output feature: its lanes walk that weight row once,
+// four values per load, against all the block's rows. Every output is summed in the same order whatever M is (a
+// lane's own values in order of k, then the lanes by butterfly), so a token's result does not depend on the batch.
+// ---------------------------------------------------------------------------------
+constexpr int SK_WARPS = 8, SK_THREADS = SK_WARPS * 32, SK_TOKENS = 8;
+
+// SPLIT false: a warp owns a feature and walks all of K. SPLIT true (few rows: decoding): a block owns ONE feature,
+// its warps walk an eighth of K each and the block adds the eight parts in warp order, so that a product of a
+// handful of rows still fills the device.
+template <typename TX, bool SPLIT>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_f32_skinny_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                       float* __restrict__ out, int M, int N, int K, long long x_stride, long long out_stride) {
+  extern __shared__ __align__(16) unsigned char sk_raw[];
+  __shared__ float parts[SK_WARPS][SK_TOKENS];
+  TX* xs = reinterpret_cast<TX*>(sk_raw);      // [SK_TOKENS][K]
+  const int m0 = blockIdx.x * SK_TOKENS, rows = min(SK_TOKENS, M - m0);
+  for (int i = threadIdx.x; i < SK_TOKENS * K; i += SK_THREADS) {
+    const int r = i / K, k = i - r * K;
+    xs[i] = r < rows ? x[(size_t)(m0 + r) * x_stride + k] : TX(0.f);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = SPLIT ? (int)blockIdx.y : (int)blockIdx.y * SK_WARPS + warp;
+  const bool live = n < N;
+  const float* wr = w + (size_t)(live ? n : 0) * K;
+  float acc[SK_TOKENS];
+#pragma unroll
+  for (int r = 0; r < SK_TOKENS; ++r) acc[r] = 0.f;
+  const int K4 = K & ~3;
+  // The piece of K this warp walks: all of it, or its eighth (in whole groups of 128).
+  const int piece = SPLIT ? (((K4 + 127) / 128 + SK_WARPS - 1) / SK_WARPS) * 128 : K4;
+  const int k_lo = SPLIT ? warp * piece : 0, k_hi = min(K4, k_lo + piece);
+  if (live) {
+    for (int k = k_lo + lane * 4; k < k_hi; k += 128) {
+      const float4 wv = *reinterpret_cast<const float4*>(wr + k);
+#pragma unroll
+      for (int r = 0; r < SK_TOKENS; ++r) {
+        const TX* xr = xs + r * K + k;
+        acc[r] = fmaf(to_float(xr[0]), wv.x, acc[r]);
+        acc[r] = fmaf(to_float(xr[1]), wv.y, acc[r]);
+        acc[r] = fmaf(to_float(xr[2]), wv.z, acc[r]);
+        acc[r] = fmaf(to_float(xr[3]), wv.w, acc[r]);
+      }
+    }
+    if (!SPLIT || warp == SK_WARPS - 1)
+      for (int k = K4 + lane; k < K; k += 32) {
+#pragma unroll
+        for (int r = 0; r < SK_TOKENS; ++r) acc[r] = fmaf(to_float(xs[r * K + k]), wr[k], acc[r]);
+      }
+  }
+#pragma unroll
+  for (int r = 0; r < SK_TOKENS; ++r) {
+    const float s = warp_sum(acc[r]);
+    if (SPLIT) {
+      if (lane == 0) parts[warp][r] = s;
+    } else if (lane == 0 && live && r < rows) {
+      out[(size_t)(m0 + r) * out_stride + n] = s + (bias ? bias[n] : 0.f);
+    }
+  }
+  if (SPLIT) {
+    __syncthreads();
+    if (threadIdx.x < rows && live) {
+      float s = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < SK_WARPS; ++wv) s += parts[wv][threadIdx.x];
+      out[(size_t)(m0 + threadIdx.x) * out_stride + n] = s + (bias ? bias[n] : 0.f);
+    }
+  }
+}
+
+// x_dtype: LLMRS_F32 or LLMRS_BF16 rows; w (16-byte aligned rows: K % 4 == 0), bias and out float32.
+LLMRS_API int llmrs_gemm_f32_skinny(const void* x, int x_dtype, long long x_stride, const float* w, const float* bias,
+                                    float* out, long long out_stride, int M, int N, int K, cudaStream_t stream) {
+  LLMRS_REQUIRE(M >= 0 && N > 0 && K > 0 && K % 4 == 0, "gemm_f32_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
+  LLMRS_REQUIRE(((uintptr_t)w & 15) == 0, "gemm_f32_skinny: the weights must be 16-byte aligned");
+  if (M == 0) return 0;
+  const size_t smem = (size_t)SK_TOKENS * K * (x_dtype == LLMRS_F32 ? 4 : 2);
+  LLMRS_REQUIRE(smem <= 200 * 1024, "gemm_f32_skinny: rows of %d values are too long", K);
+  const bool split = M <= 4 * SK_TOKENS;       // few rows: a block per feature
+  dim3 grid((M + SK_TOKENS - 1) / SK_TOKENS, split ? N : (N + SK_WARPS - 1) / SK_WARPS);
+  LLMRS_REQUIRE(grid.y <= 65535, "gemm_f32_skinny: N=%d is too large", N);
+#define LLMRS_SK_LAUNCH(T, S)                                                                                         \
+  do {                                                                                                                \
+    static size_t configured = 48 * 1024;                                                                             \
+    if (smem > configured) {                                                                                          \
+      cudaError_t e = cudaFuncSetAttribute(gemm_f32_skinny_kernel<T, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)smem);                                                                \
+      if (e != cudaSuccess) return llmrs_fail("gemm_f32_skinny: shared memory %zu: %s", smem, cudaGetErrorString(e)); \
+      configured = smem;                                                                                              \
+    }                                                                                                                 \
+    gemm_f32_skinny_kernel<T, S><<<grid, SK_THREADS, smem, stream>>>((const T*)x, w, bias, out, M, N, K, x_stride,    \
+                                                                     out_stride);                                     \
+  } while (0)
+  if (x_dtype == LLMRS_F32 && split) LLMRS_SK_LAUNCH(float, true);
+  else if (x_dtype == LLMRS_F32) LLMRS_SK_LAUNCH(float, false);
+  else if (x_dtype == LLMRS_BF16 && split) LLMRS_SK_LAUNCH(__nv_bfloat16, true);
+  else if (x_dtype == LLMRS_BF16) LLMRS_SK_LAUNCH(__nv_bfloat16, false);
+  else return llmrs_fail("gemm_f32_skinny: unknown dtype %d", x_dtype);
+#undef LLMRS_SK_LAUNCH
+  return llmrs_launch_status("gemm_f32_skinny");
+}

@@ -14,8 +14,8 @@
 //                32 at a time, with the associative form of the (max, +) recurrence, and leaves
 //                a_t = exp(f_t + m_(t-1) - m_t), b_t = exp(i_t - m_t), floor_t = exp(-m_t); m is kept per slot;
 //   prepare      q, k, v of all tokens widened to float32 (optional SiLU, q scaled, k multiplied by its gain);
-//   recurrence   a block per (request, head, 16 value columns) walks the tokens in order; four adjacent lanes share a
-//                column, each holding a quarter of its key channels in registers; rows arrive through two
+//   recurrence   a block per (request, head, 16 value columns) walks the tokens in order; four or eight adjacent lanes
+//                share a column, each holding its part of the column's key channels in registers; rows arrive through two
 //                shared-memory buffers by 16-byte asynchronous copies. A step of one token and a prompt's portion
 //                are the same kernel;
 //   output       divides by the normaliser, norms each head (or all heads together) by its root mean square,
@@ -116,16 +116,19 @@ __global__ void lr_prepare_kernel(const TA* __restrict__ q, const TA* __restrict
 // ---------------------------------------------------------------------------------
 // recurrence
 // ---------------------------------------------------------------------------------
-constexpr int LR_COLS = 16, LR_LANES = 4, LR_THREADS = LR_COLS * LR_LANES;
+constexpr int LR_COLS = 16;
 
-template <int DMAX>
-__global__ void __launch_bounds__(LR_THREADS)
+// LR_LANES adjacent lanes share a column: 4 for heads of up to 64 key channels, 8 above (16 and 32 channels per lane
+// instead of 32 and 64: shorter chains of dependent sums per token, and twice the warps on an SM that holds few blocks).
+template <int DMAX, int LR_LANES>
+__global__ void __launch_bounds__(LR_COLS * LR_LANES)
 linear_recurrence_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                          const float* __restrict__ decay, const float* __restrict__ head_decay,
                          float* __restrict__ S_all, float* __restrict__ N_all, const int* __restrict__ q_start,
                          const int* __restrict__ n_new, const int* __restrict__ slot_ids, float* __restrict__ o_raw,
                          float* __restrict__ nq, int n_heads, int dk, int dv) {
   constexpr int CHUNK = DMAX >= 256 ? 8 : 16;
+  constexpr int LR_THREADS = LR_COLS * LR_LANES;
   constexpr int IPL = DMAX / LR_LANES;             // key channels per lane
   __shared__ __align__(16) float s_q[2][CHUNK][DMAX];      // channels >= dk stay 0
   __shared__ __align__(16) float s_k[2][CHUNK][DMAX];
@@ -209,6 +212,7 @@ linear_recurrence_kernel(const float* __restrict__ Q, const float* __restrict__ 
       float o = (os[0] + os[1]) + (os[2] + os[3]);
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (LR_LANES == 8) o += __shfl_xor_sync(0xffffffffu, o, 4);
       if (part == 0 && live) {
         if (is_norm) nq[(size_t)(t0 + c0 + tt) * n_heads + head] = o;
         else o_raw[(size_t)(t0 + c0 + tt) * wv + (size_t)head * dv + col] = o;
@@ -266,13 +270,13 @@ LLMRS_API int llmrs_linear_recurrence(const void* q, const void* k, const void* 
   if (rc != 0) return rc;
   const int cols = dv + (N != nullptr ? 1 : 0);
   dim3 grid(n_requests, n_heads, (cols + LR_COLS - 1) / LR_COLS);
-#define LLMRS_LR_LAUNCH(D)                                                                                          \
-  linear_recurrence_kernel<D><<<grid, LR_THREADS, 0, stream>>>(Q, K, V, decay, head_decay, S, N, q_start, n_new,    \
-                                                               slot_ids, o_raw, nq, n_heads, dk, dv)
-  if (dk <= 32) LLMRS_LR_LAUNCH(32);
-  else if (dk <= 64) LLMRS_LR_LAUNCH(64);
-  else if (dk <= 128) LLMRS_LR_LAUNCH(128);
-  else LLMRS_LR_LAUNCH(256);
+#define LLMRS_LR_LAUNCH(D, L)                                                                                       \
+  linear_recurrence_kernel<D, L><<<grid, LR_COLS * L, 0, stream>>>(Q, K, V, decay, head_decay, S, N, q_start, n_new, \
+                                                                   slot_ids, o_raw, nq, n_heads, dk, dv)
+  if (dk <= 32) LLMRS_LR_LAUNCH(32, 4);
+  else if (dk <= 64) LLMRS_LR_LAUNCH(64, 4);
+  else if (dk <= 128) LLMRS_LR_LAUNCH(128, 8);
+  else LLMRS_LR_LAUNCH(256, 8);
 #undef LLMRS_LR_LAUNCH
   return llmrs_launch_status("linear_recurrence");
 }

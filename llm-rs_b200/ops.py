@@ -144,6 +144,10 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, block: i
     return out
 
 
+GEMM_F32_SKINNY_MAX = 264       # products with at most this many output features take the kernel laid out for them
+GEMM_F32_SKINNY_TOKENS = 8      # rows of x a block of that kernel holds in shared memory
+
+
 def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
              out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """True float32 ``x @ w.T (+ bias)`` with ``w`` of shape [N, K] (FFMA, no TF32). ``x`` may be bfloat16 rows: they
@@ -159,8 +163,15 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = No
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
     _need(out, "out", torch.float32, contiguous=False)
+    code = dtype_code(x.dtype)     # refuses any other type
+    smem = GEMM_F32_SKINNY_TOKENS * K * x.element_size()
+    if N <= GEMM_F32_SKINNY_MAX and K % 4 == 0 and smem <= 200 * 1024 and w.data_ptr() % 16 == 0:
+        # Few output features (a router, gates): the kernel that gives each feature a warp.
+        _check(_lib().llmrs_gemm_f32_skinny(_ptr(x), code, ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(bias),
+                                            _ptr(out), ctypes.c_longlong(_row_stride(out, "out")), M, N, K, _stream()),
+               "gemm_f32")
+        return out
     fn = _lib().llmrs_gemm_f32 if x.dtype == torch.float32 else _lib().llmrs_gemm_f32_bf16_rows
-    dtype_code(x.dtype)     # refuses any other type
     _check(fn(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(bias), _ptr(out),
               ctypes.c_longlong(_row_stride(out, "out")), M, N, K, _stream()), "gemm_f32")
     return out

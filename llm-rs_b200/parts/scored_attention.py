@@ -13,7 +13,8 @@ from .registry import register
 from .spec import CacheNeed, WeightSpec
 
 MASKS = {"causal": ops.MASK_CAUSAL, "window": ops.MASK_WINDOW, "chunk": ops.MASK_CHUNK}
-DECODE_SPLIT_KEYS = 256     # keys per block of the decode kernel
+DECODE_SPLIT_KEYS = 64      # keys per block of the decode kernel at least; doubled while a step has too many blocks
+DECODE_MAX_BLOCKS = 8192
 
 
 @register("mixer", "scored_attention")
@@ -133,9 +134,11 @@ class ScoredAttention(Mixer):
             ops.scored_prefill(q, out, pages, plan.arrays["prefill_tiles"], n_tiles, ctx, table, *args)
         if n_decode:
             span = max(1, min(max_kv, self.mask_size) if self.mask_size else max_kv)   # keys a query can see at most
-            splits = -(-span // DECODE_SPLIT_KEYS)
-            ops.scored_decode(q, out, pages, plan.arrays["decode_reqs"], n_decode, ctx, table, splits,
-                              DECODE_SPLIT_KEYS, *args)
+            split_keys = DECODE_SPLIT_KEYS
+            while n_decode * self.n_heads * -(-span // split_keys) > DECODE_MAX_BLOCKS and split_keys < 4096:
+                split_keys *= 2
+            ops.scored_decode(q, out, pages, plan.arrays["decode_reqs"], n_decode, ctx, table, -(-span // split_keys),
+                              split_keys, *args)
         return self.o_proj.forward(out)
 
 

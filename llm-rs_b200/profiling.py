@@ -112,7 +112,48 @@ def _cost_delta_rule(r, k, v, gate, a_raw, decay_raw, decay_bias, a_bias, norm_w
             8.0 * tokens * n_heads * d * d)
 
 
+def _cost_linear_recurrence(q, k, v, gate, norm_w, state, ctx, n_heads, dk, dv, *a, **kw):
+    # q, k, v and the gate are read, the output written; every request's state is read and written once.
+    tokens, e = q.size(0), q.element_size()
+    return (f"{tokens} tokens", tokens * n_heads * (2 * dk + 3 * dv) * e + 2 * ctx.n_requests * n_heads * dk * dv * 4,
+            4.0 * tokens * n_heads * dk * dv)
+
+
+def _scored_keys(ctx_n_new, ctx_cached, mask, size):
+    """((query, key) pairs, keys that must be read at least once) of a step, counted on the device."""
+    n, c = ctx_n_new.double(), ctx_cached.double()
+    if mask == ops.MASK_CAUSAL:
+        return (n * c + n * (n + 1) / 2).sum(), (n + c).sum()
+    # Window or chunk: a query sees size keys at most (half of that on average inside a chunk).
+    per_query = size if mask == ops.MASK_WINDOW else (size + 1) / 2
+    return (n * per_query).sum(), (n + c.clamp(max=size)).sum()
+
+
+def _cost_scored_prefill(q, out, cache, tiles, n_tiles, ctx, table, n_q_heads, n_kv_heads, dk, dv, page_size, scale,
+                         softcap, sink, mask, mask_size, **k):
+    pairs, keys = _scored_keys(ctx.n_new, ctx.cached_len, mask, mask_size)
+    per_key, fixed = n_kv_heads * (dk + dv) * cache.element_size(), _nbytes(q, out)
+    return (f"{q.size(0)} tokens", lambda: int(float(keys) * per_key) + fixed,
+            lambda: 2.0 * float(pairs) * n_q_heads * (dk + dv))
+
+
+def _cost_scored_decode(q, out, cache, dec_reqs, n_dec, ctx, table, max_splits, split_keys, n_q_heads, n_kv_heads, dk,
+                        dv, page_size, scale, softcap, sink, mask, mask_size, **k):
+    pos = ctx.cached_len[dec_reqs[:n_dec].long()].double()
+    if mask == ops.MASK_CHUNK:
+        keys = (pos - (pos / mask_size).floor() * mask_size + 1).sum()
+    else:
+        keys = ((pos + 1).clamp(max=mask_size) if mask == ops.MASK_WINDOW else pos + 1).sum()
+    per_key = n_kv_heads * (dk + dv) * cache.element_size()
+    return (f"{n_dec} requests", lambda: int(float(keys) * per_key) + n_dec * n_q_heads * (dk + dv) * 2,
+            lambda: 2.0 * float(keys) * n_q_heads * (dk + dv))
+
+
 WRAPPED: Dict[str, Callable] = {
+    "linear_recurrence": _cost_linear_recurrence, "gate_scan": _cost_rows(0), "post_norm": _cost_rows(0, 1),
+    "relu_sq": _cost_rows(0), "scale_": _cost_rows(0), "scored_prepare": _cost_rows(0, 1, 2),
+    "scored_prefill": _cost_scored_prefill, "scored_decode": _cost_scored_decode, "moe_route_top": _cost_rows(0),
+    "moe_combine_shared": _cost_rows(0, 3),
     "gemm_grouped": _cost_grouped, "gemm_batched": _cost_batched, "latent_attention": _cost_latent_attention,
     "latent_attention_prefill": _cost_latent_prefill,
     "delta_rule": _cost_delta_rule, "token_shift": _cost_rows(0), "outnorm_add": _cost_rows(0, 1),
