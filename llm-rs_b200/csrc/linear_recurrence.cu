@@ -136,7 +136,11 @@ linear_recurrence_kernel(const float* __restrict__ Q, const float* __restrict__ 
   __shared__ float s_a[2][CHUNK];
   const int req = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * LR_COLS;
   const int tid = threadIdx.x;
-  const int col = col0 + tid / LR_LANES, part = tid % LR_LANES, i0 = part * IPL;
+  const int col = col0 + tid / LR_LANES, part = tid % LR_LANES;
+  // A lane's channels come in groups of four, the groups of a column's lanes interleaved: register 4 g + e holds
+  // channel g * 4 * LR_LANES + part * 4 + e, so that the lanes' 16-byte reads of a token's row lie side by side in
+  // shared memory (a lane with one run of channels met its neighbours in the same banks).
+  auto channel = [&](int i) { return (i >> 2) * 4 * LR_LANES + part * 4 + (i & 3); };
   const int n_cols = dv + (N_all != nullptr ? 1 : 0);      // the normaliser is one more column, whose value is 1
   const bool live = col < n_cols, is_norm = col == dv;
   const int t0 = q_start[req], n = n_new[req];
@@ -148,7 +152,7 @@ linear_recurrence_kernel(const float* __restrict__ Q, const float* __restrict__ 
 #pragma unroll
   for (int i = 0; i < IPL; ++i) {
     S[i] = 0.f;
-    if (live && i0 + i < dk) S[i] = is_norm ? N_g[i0 + i] : S_g[(size_t)(i0 + i) * dv + col];
+    if (live && channel(i) < dk) S[i] = is_norm ? N_g[channel(i)] : S_g[(size_t)channel(i) * dv + col];
   }
   for (int e = tid; e < 2 * CHUNK * DMAX; e += LR_THREADS) {
     (&s_q[0][0][0])[e] = 0.f;
@@ -198,8 +202,8 @@ linear_recurrence_kernel(const float* __restrict__ Q, const float* __restrict__ 
       float os[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < IPL; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][i0 + i]);
-        const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][i0 + i]);
+        const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][i * LR_LANES + part * 4]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][i * LR_LANES + part * 4]);
         S[i] = fmaf(k4.x, vj, a * S[i]);
         S[i + 1] = fmaf(k4.y, vj, a * S[i + 1]);
         S[i + 2] = fmaf(k4.z, vj, a * S[i + 2]);
@@ -223,9 +227,9 @@ linear_recurrence_kernel(const float* __restrict__ Q, const float* __restrict__ 
   if (live) {
 #pragma unroll
     for (int i = 0; i < IPL; ++i)
-      if (i0 + i < dk) {
-        if (is_norm) N_g[i0 + i] = S[i];
-        else S_g[(size_t)(i0 + i) * dv + col] = S[i];
+      if (channel(i) < dk) {
+        if (is_norm) N_g[channel(i)] = S[i];
+        else S_g[(size_t)channel(i) * dv + col] = S[i];
       }
   }
 }

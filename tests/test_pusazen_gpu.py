@@ -186,8 +186,8 @@ def test_matrix_memory_mixer_against_plain(dtype, heads, dk, dv, cap):
             got[r].append(y[o:o + n])
             o += n
             at[r] += n
-    for r in range(3):
-        _close(torch.cat(got[r]), want[r], dtype, r, bf16=0.04)
+    for r in range(3):      # (float32: one row of the 100-channel case magnifies rounding a thousandfold, see _close)
+        _close(torch.cat(got[r]), want[r], dtype, r, f32=1e-4, bf16=0.04)
     assert all(torch.all(t[1] == 0) and torch.all(t[3] == 0) for t in state.values())
 
 
