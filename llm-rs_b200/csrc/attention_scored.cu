@@ -38,6 +38,37 @@ __device__ __forceinline__ float capped(const ScoreOpts& o, float s) {
   s *= o.scale;
   return o.softcap > 0.f ? o.softcap * tanhf(s / o.softcap) : s;
 }
+// For the tensor-core kernel: 2^x and 1/x by the hardware's approximations (relative errors 2^-22 and one unit in the
+// last place), and the soft cap built on them, cap * tanh(s / cap) = cap - 2 cap / (2^(2 s log2(e) / cap) + 1), in the
+// softmax's base-2 scale: a product, an exponential, a sum, a reciprocal and a fused multiply-add per score. The absolute
+// error is that of a float32 number of the cap's size (the subtraction from cap rounds there whatever the method); all of
+// it is float32 arithmetic. The kernel for any type keeps tanhf and expf.
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_fast(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+struct FastCap {
+  float in, out;      // score * in -> exponent; cap * log2(e) = out
+  bool on;
+  __device__ __forceinline__ FastCap(const ScoreOpts& o) {
+    constexpr float LOG2E = 1.4426950408889634f;
+    on = o.softcap > 0.f;
+    in = on ? o.scale * 2.0f * LOG2E / o.softcap : o.scale * LOG2E;
+    out = o.softcap * LOG2E;
+  }
+  // The capped score times log2(e).
+  __device__ __forceinline__ float operator()(float s) const {
+    const float t = s * in;
+    if (!on) return t;
+    return fmaf(rcp_fast(ex2_fast(fminf(t, 80.0f)) + 1.0f), -2.0f * out, out);
+  }
+};
 __device__ __host__ __forceinline__ size_t page_head_offset(int page, int kvh, int n_kv_heads, int page_size, int dk,
                                                             int dv) {
   return ((size_t)page * n_kv_heads + kvh) * (size_t)page_size * (dk + dv);
@@ -276,7 +307,7 @@ using bf16 = __nv_bfloat16;
 constexpr int SM_BQ = 64, SM_BK = 64, SM_WARPS = 4, SM_THREADS = SM_WARPS * 32;
 
 template <int KCH, int VCH>
-__global__ void __launch_bounds__(SM_THREADS)
+__global__ void __launch_bounds__(SM_THREADS, (KCH <= 8 && VCH <= 8) ? 3 : 1)
 scored_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                           const bf16* __restrict__ cache, const int* __restrict__ tiles,
                           const int* __restrict__ q_start, const int* __restrict__ n_new,
@@ -352,6 +383,8 @@ scored_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* 
   const int pos_r[2] = {pos0 + warp * 16 + gq, pos0 + warp * 16 + gq + 8};
   const int lo_r[2] = {first_visible(opt, pos_r[0]), first_visible(opt, pos_r[1])};
   const int warp_lo = first_visible(opt, pos0 + warp * 16);      // first_visible never falls as the position grows
+  const int last_lo = first_visible(opt, pos0 + warp * 16 + 15);
+  const FastCap cap(opt);
   constexpr float LOG2E = 1.4426950408889634f;
 
   int stage = 0;
@@ -378,15 +411,28 @@ scored_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* 
         }
       }
       float mx[2] = {-INFINITY, -INFINITY};
+      // Only a tile that touches the diagonal, or in which some row's first visible key lies, has scores to hide.
+      const int pw = pos0 + warp * 16;
+      const bool need_mask = kb + SM_BK - 1 > pw || kb < last_lo;
+      if (need_mask) {
 #pragma unroll
-      for (int n = 0; n < SM_BK / 8; ++n)
+        for (int n = 0; n < SM_BK / 8; ++n)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = kb + n * 8 + tq * 2 + (e & 1);
-          const bool seen = key <= pos_r[e >> 1] && key >= lo_r[e >> 1];
-          s[n][e] = seen ? capped(opt, s[n][e]) * LOG2E : -INFINITY;
-          mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
-        }
+          for (int e = 0; e < 4; ++e) {
+            const int key = kb + n * 8 + tq * 2 + (e & 1);
+            const bool seen = key <= pos_r[e >> 1] && key >= lo_r[e >> 1];
+            s[n][e] = seen ? cap(s[n][e]) : -INFINITY;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+          }
+      } else {
+#pragma unroll
+        for (int n = 0; n < SM_BK / 8; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s[n][e] = cap(s[n][e]);
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+          }
+      }
       float corr[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
@@ -394,14 +440,14 @@ scored_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* 
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(m_row[r], mx[r]);
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
-        corr[r] = exp2f(m_row[r] - m_use);
+        corr[r] = ex2_fast(m_row[r] - m_use);
         m_row[r] = m_new;
         float sum = 0.f;
 #pragma unroll
         for (int n = 0; n < SM_BK / 8; ++n)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const float p = exp2f(s[n][r * 2 + e] - m_use);
+            const float p = ex2_fast(s[n][r * 2 + e] - m_use);
             s[n][r * 2 + e] = p;
             sum += p;
           }
@@ -440,8 +486,8 @@ scored_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* 
       float w = 1.0f, l = l_row[r];
       if (opt.sink) {
         const float sk = opt.sink[head] * LOG2E, mf = fmaxf(m_row[r], sk);
-        w = exp2f(m_row[r] - mf);
-        l = l * w + exp2f(sk - mf);
+        w = ex2_fast(m_row[r] - mf);
+        l = l * w + ex2_fast(sk - mf);
       }
       const float inv = l > 0.f ? w / l : 0.f;
       bf16* orow = out + (size_t)(tok0 + row) * out_stride + (size_t)head * DV;

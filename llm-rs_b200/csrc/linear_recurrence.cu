@@ -23,6 +23,9 @@
 #include "common.cuh"
 #include "mma_util.cuh"
 
+__device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr(dst)), "l"(src));
+}
 __device__ __forceinline__ float lr_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float lr_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
@@ -177,12 +180,17 @@ linear_recurrence_kernel(const float* __restrict__ Q, const float* __restrict__ 
         (which ? s_k : s_q)[buf][tt][i] = (which ? K : Q)[src];
       }
     }
+    // Values and decays by 4-byte asynchronous copies too: a plain load would hold the warp for a memory round trip
+    // at the top of every chunk, before it starts on the tokens it already has.
     for (int e = tid; e < cn * LR_COLS; e += LR_THREADS) {
       const int tt = e / LR_COLS, c = col0 + e % LR_COLS;
-      s_v[buf][tt][e % LR_COLS] = c < dv ? V[(size_t)(t0 + c0 + tt) * wv + (size_t)head * dv + c] : 1.0f;
+      if (c < dv) cp_async_4(&s_v[buf][tt][e % LR_COLS], V + (size_t)(t0 + c0 + tt) * wv + (size_t)head * dv + c);
+      else s_v[buf][tt][e % LR_COLS] = 1.0f;
     }
-    for (int tt = tid; tt < cn; tt += LR_THREADS)
-      s_a[buf][tt] = decay ? decay[(size_t)(t0 + c0 + tt) * n_heads + head] : a_head;
+    for (int tt = tid; tt < cn; tt += LR_THREADS) {
+      if (decay) cp_async_4(&s_a[buf][tt], decay + (size_t)(t0 + c0 + tt) * n_heads + head);
+      else s_a[buf][tt] = a_head;
+    }
     cp_async_commit();
   };
 
