@@ -89,9 +89,20 @@ PUSAZEN_E = {
         (_attention(6, 3, 16, 16, 0.3, chunk=33, rot=(1e5, 16)), None),
         (_memory(2, 32, 32, 10.0), _moe(32, 4, 2, shared=32)))}
 
+# Sizes that are multiples of nothing: a width of 100, heads of 12 x 20 and 80 x 48 (no tensor-core kernel is built for
+# the first), a chunk of 5, rotation of 2 channels and of all 80, every expert chosen (5 of 5), two experts with one
+# chosen, a vocabulary of 61, alpha below 1.
+PUSAZEN_F = {
+    "architecture": "Pusazen", "vocab": 61, "width": 100, "norm": {"eps": 1e-6}, "postln_alpha": 0.7, "logit_scale": 2.0,
+    "layers": _layers(
+        (_attention(3, 3, 12, 20, 0.33, chunk=5, softcap=50.0, rot=(77.0, 2)), _moe(28, 5, 5, shared=12)),
+        (_memory(5, 12, 20, 2.5), _dense(36)),
+        (_lightning(2, 36, 52, (0.7, 0.98)), None),
+        (_attention(8, 2, 80, 48, 0.1, chunk=64, rot=(1e4, 80)), _moe(20, 2, 1)))}
+
 # name -> (config.json, seed, sigma of matrices, page size)
 PUSAZEN = {"A": (PUSAZEN_A, 3, 0.15, 16), "B": (PUSAZEN_B, 4, 0.15, 8), "C": (PUSAZEN_C, 5, 0.06, 16),
-           "D": (PUSAZEN_D, 6, 0.2, 16), "E": (PUSAZEN_E, 7, 0.15, 32)}
+           "D": (PUSAZEN_D, 6, 0.2, 16), "E": (PUSAZEN_E, 7, 0.15, 32), "F": (PUSAZEN_F, 8, 0.12, 16)}
 
 
 def write_pusazen_model(name: str, folder: str, dtype=torch.bfloat16) -> str:

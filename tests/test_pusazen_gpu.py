@@ -23,7 +23,7 @@ TOL_F32 = 2e-4          # float32 engine against float64: rounding only
 TOL_BF16_REL = 0.05     # of the largest logit; a wrong key, state or expert moves logits by their own size
 DEV = "cuda:0"
 LENGTHS = {"A": [2, 19, 40, 77, 131, 260], "B": [1, 9, 33, 70, 128, 161], "C": [5, 31, 66, 150, 300],
-           "D": [1, 2, 18, 65, 140], "E": [3, 16, 47, 90, 200]}
+           "D": [1, 2, 18, 65, 140], "E": [3, 16, 47, 90, 200], "F": [1, 6, 29, 64, 133, 210]}
 MODES = ["whole", "tail", "portions", "mixed"]
 
 
