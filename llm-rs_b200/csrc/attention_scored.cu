@@ -519,6 +519,15 @@ static int launch_scored_mma(const void* q, long long q_stride, void* out, long 
   return llmrs_launch_status("scored_prefill_mma");
 }
 
+// The tcgen05 kernel of attention_tc.cu (keys and values of 128 channels, long portions).
+bool llmrs_attn_prefill_tc_supported(const void* q, long long q_stride, const void* cache, int d, int page_size,
+                                     float scale);
+int llmrs_attn_prefill_tc_scored(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
+                                 const void* cache, long long cache_rows, const int* tiles, int n_tiles,
+                                 const int* q_start, const int* n_new, const int* cached_len, const int* block_table,
+                                 int table_stride, int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
+                                 float softcap, const float* sink, int chunk, int* error_flag, cudaStream_t stream);
+
 static int g_scored_generic_only = 0;
 // 1: bfloat16 also takes the kernel for any type (tests compare the two).
 LLMRS_API void llmrs_scored_generic_only(int on) { g_scored_generic_only = on; }
@@ -533,7 +542,7 @@ LLMRS_API int llmrs_scored_prefill(const void* q, long long q_stride, void* out,
                                    const int* n_new, const int* cached_len, const int* block_table, int table_stride,
                                    int n_q_heads, int n_kv_heads, int dk, int dv, int page_size, float scale,
                                    float softcap, const float* sink, int mask, int mask_size, int dtype,
-                                   cudaStream_t stream) {
+                                   int n_tokens, int n_pages, int prefer_tc, cudaStream_t stream) {
   LLMRS_REQUIRE(n_tiles >= 0 && n_q_heads > 0 && n_kv_heads > 0 && page_size > 0, "scored_prefill: bad sizes");
   LLMRS_REQUIRE(n_q_heads % n_kv_heads == 0, "scored_prefill: %d query heads are no multiple of %d key heads",
                 n_q_heads, n_kv_heads);
@@ -544,6 +553,17 @@ LLMRS_API int llmrs_scored_prefill(const void* q, long long q_stride, void* out,
   if (n_tiles == 0) return 0;
   ScoreOpts opt{scale, softcap, sink, mask, mask_size};
   if ((long long)n_tiles * n_q_heads > 2147483647LL) return llmrs_fail("scored_prefill: %d tiles are too many", n_tiles);
+  // Long portions of heads of 128 channels: the tcgen05 kernel (128-query blocks, K and V by TMA, scores in tensor
+  // memory), with the cap, the sink and the mask in its softmax threads. Its waits are bounded; a block that gives
+  // up leaves a code that llmrs_attention_tc_error reads.
+  if (dtype == LLMRS_BF16 && prefer_tc && !g_scored_generic_only && dk == 128 && dv == 128 && n_tiles <= 8192 &&
+      out_stride % 8 == 0 && ((uintptr_t)out & 15) == 0 &&
+      llmrs_attn_prefill_tc_supported(q, q_stride, cache, dk, page_size, scale))
+    return llmrs_attn_prefill_tc_scored(q, q_stride, n_tokens, out, out_stride, cache,
+                                        (long long)n_pages * n_kv_heads * 2 * page_size, tiles, n_tiles, q_start, n_new,
+                                        cached_len, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
+                                        mask == MASK_WINDOW ? mask_size : 0, scale, softcap, sink,
+                                        mask == MASK_CHUNK ? mask_size : 0, nullptr, stream);
   if (dtype == LLMRS_BF16 && !g_scored_generic_only && q_stride % 2 == 0 && out_stride % 2 == 0) {
 #define LLMRS_SM_CASE(K, V)                                                                                     \
   if (dk == 16 * K && dv == 16 * V)                                                                              \

@@ -170,6 +170,11 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&v)[3
         "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -194,13 +199,19 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
 //   o[2]           O += P V of a tile is done
 // Barriers that are used every tile come in pairs, one per parity of the tile: the roles run up to
 // two tiles apart, and a wait by parity must never be a whole phase behind its barrier.
+// SCORED false: no cap, no sink, no chunks (the arguments are ignored and the code for them is not there).
+template <bool SCORED>
 __global__ void __launch_bounds__(AT_THREADS + 96, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, long long q_stride,
                        bf16* __restrict__ out, long long out_stride, const int* __restrict__ tiles,
                        const int* __restrict__ q_start, const int* __restrict__ n_new,
                        const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
                        int n_list, int persistent, int n_q_heads, int n_kv_heads, int page_size, int box_rows, int window, float scale,
+                       float softcap_, const float* __restrict__ sink_, int chunk_,
                        int* __restrict__ error_flag, uint32_t wait_limit, int test_skip_tile) {
+  const float softcap = SCORED ? softcap_ : 0.f;
+  const float* sink = SCORED ? sink_ : nullptr;
+  const int chunk = SCORED ? chunk_ : 0;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = smem_raw;           // 1024-byte aligned (checked below): the swizzle pattern needs it
   unsigned char* KV = base;                 // AT_STAGES x (K: 2 halves of [64 keys][64 dims], then V the same)
@@ -257,7 +268,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     it.tok0 = q_start[req] + q_off;
     it.pos0 = cached_len[req] + q_off;
     it.kv_hi = it.pos0 + it.rows;
-    it.key_floor = window > 0 ? max(0, it.pos0 - window + 1) : 0;
+    // The first key the item's first row may see: its chunk's first position, or the window's far edge.
+    it.key_floor = chunk > 0 ? (it.pos0 / chunk) * chunk : (window > 0 ? max(0, it.pos0 - window + 1) : 0);
     it.kv_lo = (it.key_floor / AT_BK) * AT_BK;
     it.n_tiles = (it.kv_hi - it.kv_lo + AT_BK - 1) / AT_BK;
     it.table = block_table + (size_t)req * table_stride;
@@ -426,7 +438,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     // ---- softmax threads ------------------------------------------------------------------
     const int row = tid;                      // this thread's query row = its lane of tensor memory
     const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-    const float sl2 = scale * AT_LOG2E;
+    // With a soft cap the scores are turned into cap * tanh(s * scale / cap) * log2(e) first, as
+    // cap' - 2 cap' / (2^(2 s scale log2(e) / cap) + 1) from the hardware's 2^x and 1/x (relative errors 2^-22 and one
+    // unit in the last place), and the softmax below takes them as they are.
+    const bool capped = softcap > 0.f;
+    const float cap_in = capped ? scale * 2.0f * AT_LOG2E / softcap : 0.f, cap_out = softcap * AT_LOG2E;
+    const float sl2 = capped ? 1.0f : scale * AT_LOG2E;
     int g0 = 0;
     bool ok = true;
     for (int r = 0; ok; ++r) {
@@ -455,6 +472,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         bar_arrive(bar_q);
       }
       const int my_pos = pos0 + row;
+      const int my_lo = chunk > 0 ? (my_pos / chunk) * chunk : 0;                   // chunks count from position 0
+      const int last_lo = chunk > 0 ? ((pos0 + AT_BQ - 1) / chunk) * chunk : 0;     // the last row's first visible key
       float m_ref = -INFINITY, l_sum = 0.f;
       for (int j = 0; j < n_tiles; ++j) {
         const int g = g0 + j;
@@ -472,12 +491,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
 #pragma unroll
           for (int e = 0; e < 32; ++e) s[c + e] = t0[e];
         }
-        const bool need_mask = kb + AT_BK - 1 > pos0 || (window > 0 && kb <= pos0 + AT_BQ - 1 - window);
+        if (capped) {
+#pragma unroll
+          for (int c = 0; c < AT_BK; ++c) s[c] = fmaf(rcp_approx(ex2(fminf(s[c] * cap_in, 80.0f)) + 1.0f), -2.0f * cap_out, cap_out);
+        }
+        const bool need_mask = kb + AT_BK - 1 > pos0 || (window > 0 && kb <= pos0 + AT_BQ - 1 - window) || kb < last_lo;
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < AT_BK; ++c) {
             const int key = kb + c;
-            const bool seen = key <= my_pos && (window <= 0 || key > my_pos - window);
+            const bool seen = key <= my_pos && (window <= 0 || key > my_pos - window) && key >= my_lo;
             s[c] = seen ? s[c] : -INFINITY;
           }
         }
@@ -542,6 +565,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
       fence_after();
       if (ok) {
         // Every thread reads its row of O (the load is warp-wide); rows past the portion's end are not stored.
+        // A sink is one more term of the denominator, with no key and no value, against the same reference.
+        if (sink != nullptr && m_ref != -INFINITY) l_sum += ex2(fminf(sink[it.head] * AT_LOG2E - m_ref, 126.0f));
         const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
         bf16* orow = out + (size_t)(it.tok0 + row) * out_stride + (size_t)it.head * AT_D;
 #pragma unroll 1
@@ -648,11 +673,29 @@ bool llmrs_attn_prefill_tc_supported(const void* q, long long q_stride, const vo
 
 // Prefill attention on tcgen05 (see the head of this file). `n_tokens` is the number of rows of q,
 // `cache_rows` = n_pages * n_kv_heads * 2 * page_size the number of head_dim-wide rows of the cache.
+// With options on the score (softcap > 0: cap * tanh(score / cap); sink: one number per query head in the softmax's
+// denominator, or null; chunk > 0: a query sees the keys of its own chunk of that many positions only).
+int llmrs_attn_prefill_tc_scored(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
+                                 const void* cache, long long cache_rows, const int* tiles, int n_tiles,
+                                 const int* q_start, const int* n_new, const int* cached_len, const int* block_table,
+                                 int table_stride, int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
+                                 float softcap, const float* sink, int chunk, int* error_flag, cudaStream_t stream);
+
 int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
                           const void* cache, long long cache_rows, const int* tiles, int n_tiles, const int* q_start,
                           const int* n_new, const int* cached_len, const int* block_table, int table_stride,
                           int n_q_heads, int n_kv_heads, int page_size, int window, float scale, int* error_flag,
                           cudaStream_t stream) {
+  return llmrs_attn_prefill_tc_scored(q, q_stride, n_tokens, out, out_stride, cache, cache_rows, tiles, n_tiles, q_start,
+                                      n_new, cached_len, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
+                                      window, scale, 0.f, nullptr, 0, error_flag, stream);
+}
+
+int llmrs_attn_prefill_tc_scored(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
+                                 const void* cache, long long cache_rows, const int* tiles, int n_tiles,
+                                 const int* q_start, const int* n_new, const int* cached_len, const int* block_table,
+                                 int table_stride, int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
+                                 float softcap, const float* sink, int chunk, int* error_flag, cudaStream_t stream) {
   CUtensorMap map_kv;
   int rc;
   (void)n_tokens;
@@ -660,11 +703,13 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
   const int box_rows = page_size % 64 == 0 ? 64 : 16;
   if ((rc = make_map(&map_kv, cache, cache_rows, AT_D, AT_D, box_rows))) return rc;
   const size_t smem = AT_STAGES * STAGE_BYTES + (4 * AT_STAGES + 8) * 8 + 16 + 2 * AT_MAX_LIST;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const bool scored = softcap > 0.f || sink != nullptr || chunk > 0;
+  static bool configured[2] = {false, false};
+  if (!configured[scored]) {
+    cudaError_t e = scored ? cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                           : cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return llmrs_fail("attn_prefill_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    configured = true;
+    configured[scored] = true;
   }
   // A block holds all of tensor memory, so an SM runs one at a time. With up to 16 items per SM one block per SM
   // walks its share of them, and an item's start runs under the end of the item before (one prompt of 1,024 /
@@ -682,10 +727,15 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
   const long long n_lin = (long long)n_q_heads * n_tiles, n_items = (long long)n_q_heads * ((n_tiles + 1) / 2);
   const int persistent = n_items > n_sm && n_items <= 16LL * n_sm ? 1 : 0;
   dim3 grid((unsigned)(persistent ? n_sm : n_lin));
-  attn_prefill_tc_kernel<<<grid, AT_THREADS + 96, smem, stream>>>(map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
-                                                              tiles, q_start, n_new, cached_len, block_table,
-                                                              table_stride, n_tiles, persistent, n_q_heads, n_kv_heads, page_size,
-                                                              box_rows, window, scale, error_flag, g_wait_limit,
-                                                              g_test_skip_tile);
+  if (scored)
+    attn_prefill_tc_kernel<true><<<grid, AT_THREADS + 96, smem, stream>>>(
+        map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride, tiles, q_start, n_new, cached_len, block_table,
+        table_stride, n_tiles, persistent, n_q_heads, n_kv_heads, page_size, box_rows, window, scale, softcap, sink, chunk,
+        error_flag, g_wait_limit, g_test_skip_tile);
+  else
+    attn_prefill_tc_kernel<false><<<grid, AT_THREADS + 96, smem, stream>>>(
+        map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride, tiles, q_start, n_new, cached_len, block_table,
+        table_stride, n_tiles, persistent, n_q_heads, n_kv_heads, page_size, box_rows, window, scale, 0.f, nullptr, 0,
+        error_flag, g_wait_limit, g_test_skip_tile);
   return llmrs_launch_status("attn_prefill_tc");
 }

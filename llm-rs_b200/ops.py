@@ -1082,8 +1082,11 @@ def scored_generic_only(on: bool) -> None:
 
 
 def scored_prefill(q, out, cache, tiles, n_tiles: int, ctx, table, n_q_heads: int, n_kv_heads: int, dk: int, dv: int,
-                   page_size: int, scale: float, softcap: float, sink, mask: int, mask_size: int) -> None:
-    """Prompt portions (tiles of 64 queries: request, offset) through ``csrc/attention_scored.cu``."""
+                   page_size: int, scale: float, softcap: float, sink, mask: int, mask_size: int,
+                   prefer_tc: bool = False) -> None:
+    """Prompt portions (tiles of 64 queries: request, offset) through ``csrc/attention_scored.cu``. ``prefer_tc`` asks
+    for the tcgen05 kernel where it applies (bfloat16, keys and values of 128 channels, pages of a multiple of 16
+    keys; worth it when the portions are long)."""
     _need(q, "q", contiguous=False)
     _need(out, "out", q.dtype, contiguous=False)
     _need(cache, "cache", q.dtype)
@@ -1091,7 +1094,7 @@ def scored_prefill(q, out, cache, tiles, n_tiles: int, ctx, table, n_q_heads: in
         _ptr(q), _LL(_row_stride(q, "q")), _ptr(out), _LL(_row_stride(out, "out")), _ptr(cache), _ptr(tiles), n_tiles,
         _ptr(ctx.q_start), _ptr(ctx.n_new), _ptr(ctx.cached_len), _ptr(table), table.size(1), n_q_heads, n_kv_heads,
         dk, dv, page_size, ctypes.c_float(scale), ctypes.c_float(softcap), _ptr(sink), mask, mask_size,
-        dtype_code(q.dtype), _stream()), "scored_prefill")
+        dtype_code(q.dtype), q.size(0), cache.size(0), int(prefer_tc), _stream()), "scored_prefill")
 
 
 def scored_decode(q, out, cache, dec_reqs, n_dec: int, ctx, table, max_splits: int, split_keys: int, n_q_heads: int,

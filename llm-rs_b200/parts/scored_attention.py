@@ -6,7 +6,7 @@ from typing import Optional
 import torch
 
 from .. import host, ops
-from .attention import PREFILL_TILE
+from .attention import _ATTN_TC, PREFILL_TILE
 from .base import Mixer, Plan, Runtime, StepInfo
 from .linear import Linear
 from .registry import register
@@ -34,8 +34,10 @@ class ScoredAttention(Mixer):
     Scores, weights, norms, positions and angles are float32 (angles are made in double). Pages: a group of kind
     "window" for the masks that bound how far back a query reads (a chunk never reaches further back than
     ``mask_size`` - 1 keys), else "full"; a token stores ``dim`` + ``vdim`` numbers per key head. Prompt portions run
-    on the tensor cores in bfloat16 (``csrc/attention_scored.cu``); requests that bring one token take the decode
-    kernel in the same step. ``names`` maps the roles q, k, v, o, q_norm, k_norm, sink."""
+    on the tensor cores in bfloat16 (``csrc/attention_scored.cu``: ``mma.sync``; long portions of heads of 128
+    channels: the tcgen05 kernel of ``csrc/attention_tc.cu``, which takes the cap, the sink and the mask in its
+    softmax; ``LLMRS_ATTN_TC=0`` keeps ``mma.sync``); requests that bring one token take the decode kernel in the
+    same step. ``names`` maps the roles q, k, v, o, q_norm, k_norm, sink."""
     ROLES = ("q", "k", "v", "o", "q_norm", "k_norm", "sink")
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
@@ -131,7 +133,8 @@ class ScoredAttention(Mixer):
         args = (self.n_heads, self.n_kv_heads, self.dim, self.vdim, cache.page_size, self.scale, self.softcap,
                 self.sink, mask, self.mask_size)
         if n_tiles:
-            ops.scored_prefill(q, out, pages, plan.arrays["prefill_tiles"], n_tiles, ctx, table, *args)
+            ops.scored_prefill(q, out, pages, plan.arrays["prefill_tiles"], n_tiles, ctx, table, *args,
+                               prefer_tc=bool(plan.values["long_portions"]) and _ATTN_TC)
         if n_decode:
             span = max(1, min(max_kv, self.mask_size) if self.mask_size else max_kv)   # keys a query can see at most
             split_keys = DECODE_SPLIT_KEYS

@@ -315,6 +315,52 @@ def test_attention_mixer_against_plain(dtype, heads, kv, dk, dv, size, cap, rot,
         _close(torch.cat(got[r]), want[r], dtype, r)
 
 
+@pytest.mark.parametrize("heads,kv,size,cap,sink,page", [(4, 2, 96, 30.0, True, 16), (2, 2, 0, 0.0, True, 64), (4, 1, 200, 5.0, False, 16),
+                                                     (2, 1, 128, 0.0, False, 32), (3, 3, 1, 8.0, True, 16)])
+def test_long_portions_of_heads_of_128_on_tcgen05(heads, kv, size, cap, sink, page):
+    """Portions of some hundred tokens with keys and values of 128 channels take the tcgen05 kernel (128-query blocks),
+    with the cap, the sink and the chunk mask in its softmax: two requests in two steps each, the second continuing
+    from the pages, chunk edges inside a block of queries and on its edge; against the plain implementation, and the
+    same steps through the mma.sync kernel must agree with it to bfloat16's rounding."""
+    from llm_rs_b200 import ops
+    from llm_rs_b200.parts import scored_attention
+    dtype = torch.bfloat16
+    outs = {}
+    for tc in (True, False):
+        part, w, planes, m, g, D = _attention_setup(dtype, heads, kv, 128, 128, "chunk" if size else "causal", size, cap,
+                                                    64, page, 64, 31 + heads, sink=sink)
+        lens = [430, 260]
+        seqs = [torch.randn(n, D, generator=g).bfloat16().float() for n in lens]
+        wd = {k: v.double() for k, v in w.items()}
+        wd.setdefault("m.sink", torch.full((heads,), -1e30, dtype=torch.float64))
+        want = [P.attention(s.double(), wd, "m.", m, 1e-5) for s in seqs]
+        perm = torch.randperm(64, generator=g).tolist()
+        width = -(-max(lens) // page)
+        table = torch.tensor([perm[:width], (perm[width:] + perm[:width])[:width]], dtype=torch.int32, device=DEV)
+        cache = SimpleNamespace(planes=planes, block_table=table, page_size=page, owns=True, state={})
+        at, got = [0, 0], [[], []]
+        old = scored_attention._ATTN_TC
+        scored_attention._ATTN_TC = tc
+        try:
+            for cut in [(300, 130), (130, 130)]:
+                ctx = _ctx(list(cut), list(at), planner=part, page_size=page)
+                assert ctx.plans[part.plan_key()].values["long_portions"]
+                x = torch.cat([s[a:a + n] for s, a, n in zip(seqs, at, cut)]).to(DEV, dtype)
+                y = part.forward(x, ctx, cache).float().cpu()
+                o = 0
+                for r, n in enumerate(cut):
+                    got[r].append(y[o:o + n])
+                    o += n
+                    at[r] += n
+        finally:
+            scored_attention._ATTN_TC = old
+        ops.check_attention_error()
+        for r in range(2):
+            _close(torch.cat(got[r]), want[r], dtype, (tc, r))
+        outs[tc] = torch.cat(got[0] + got[1])
+    assert (outs[True] - outs[False]).abs().max().item() <= 0.03 * outs[False].abs().max().item()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("decode", [False, True])
 def test_chunk_edges(dtype, decode):
