@@ -177,6 +177,22 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = No
     return out
 
 
+F32_ROWS_LIBRARY_MIN = 33     # steps of at least this many rows send ``product_f32`` of bfloat16 operands to the library
+
+
+def product_f32(x: torch.Tensor, w_stored: torch.Tensor, w_f32: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """A product whose result must not be rounded below float32 (a router's logits, the gates of a recurrence):
+    ``x @ w.T + bias`` as float32. ``w_stored`` is the weight as the folder stores it, ``w_f32`` the same widened.
+    When the rows AND the stored weight are bfloat16, every product of two operands is exact in float32, so a
+    tensor-core product with float32 accumulation and float32 output computes the same sum as the FFMA kernel up to
+    the order of its terms: prompt portions take it (the library's, as the other products of large steps); steps of
+    few rows and everything else take ``gemm_f32``."""
+    if (x.dtype == torch.bfloat16 and w_stored.dtype == torch.bfloat16 and x.size(0) >= F32_ROWS_LIBRARY_MIN
+            and x.is_contiguous()):
+        return library_gemm(x, w_stored, bias, torch.float32)
+    return gemm_f32(x, w_f32, bias)
+
+
 def library_gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x @ w.T (+ bias)`` in bfloat16 through the library (cuBLAS via ``torch``): the products of steps with

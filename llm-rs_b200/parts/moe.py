@@ -90,7 +90,7 @@ class MixtureOfExperts(FeedForward):
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
         if len({self.w_gate.dtype, self.w_up.dtype, self.w_down.dtype}) != 1:
             self.w_gate, self.w_up, self.w_down = (w.to(torch.float32) for w in (self.w_gate, self.w_up, self.w_down))
-        self.table = self.router_w = self.router_b = self.shared = None
+        self.table = self.router_w = self.router_w_stored = self.router_b = self.shared = None
         if self.router == "table":
             self.table = tensors[self.prefix + self.names["table"]].contiguous()
             bad = (self.table < 0) | (self.table >= self.n_experts)
@@ -98,13 +98,17 @@ class MixtureOfExperts(FeedForward):
                 raise ValueError(f"{self.prefix}{self.names['table']} names experts outside 0..{self.n_experts - 1}")
         rows, bias = [], []
         if self.router == "linear":
-            rows.append(tensors[self.prefix + self.names["router"]].to(torch.float32))
+            rows.append(tensors[self.prefix + self.names["router"]])
             bias.append(tensors[self.prefix + self.names["router_bias"]].to(torch.float32))
         if self.shared_gated:       # the shared expert's gate is one more row of the router's product
-            rows.append(tensors[self.prefix + self.names["shared_gate"]].to(torch.float32))
+            rows.append(tensors[self.prefix + self.names["shared_gate"]])
             bias.append(torch.zeros((1,), dtype=torch.float32, device=rows[-1].device))
         if rows:
-            self.router_w, self.router_b = torch.cat(rows, dim=0).contiguous(), torch.cat(bias, dim=0).contiguous()
+            self.router_w = torch.cat([r.to(torch.float32) for r in rows], dim=0).contiguous()
+            self.router_b = torch.cat(bias, dim=0).contiguous()
+            # The same rows as the folder stores them (see ``ops.product_f32``).
+            same = all(r.dtype == rows[0].dtype for r in rows)
+            self.router_w_stored = torch.cat(rows, dim=0).contiguous() if same else self.router_w
         if self.shared_size:
             from .mlp import SwiGLU
             sp = self.prefix + self.names["shared"]
@@ -115,7 +119,8 @@ class MixtureOfExperts(FeedForward):
         """x: the step's rows, float32 (the residual stream) or the activation type. Returns float32 [tokens, hidden]."""
         if self.act_dtype == torch.bfloat16 and x.dtype == torch.float32:
             x = ops.token_shift(x, None, None, None, torch.bfloat16)     # the rows as activations: the tensor cores' type
-        logits = ops.gemm_f32(x, self.router_w, self.router_b) if self.router_w is not None else None
+        logits = (ops.product_f32(x, self.router_w_stored, self.router_w, self.router_b)
+                  if self.router_w is not None else None)
         if self.router == "table":
             expert_of, weight_of = ops.moe_route_table(ctx.token_ids, self.table, self.n_experts)
         else:

@@ -90,6 +90,8 @@ class MatrixMemory(_MatrixStateMixer):
         # The gates' product is float32 whatever the activation type: what enters the recurrence is not rounded.
         self.gate_w = torch.cat([f32("i"), f32("f")], dim=0).contiguous()
         self.gate_b = torch.cat([f32("i_bias"), f32("f_bias")], dim=0).contiguous()
+        stored = [tensors[nm("i")], tensors[nm("f")]]       # as the folder stores them (see ``ops.product_f32``)
+        self.gate_w_stored = torch.cat(stored, dim=0).contiguous() if stored[0].dtype == stored[1].dtype else self.gate_w
 
     def state_need(self):
         return StateNeed({self.STATE: (self.n_heads, self.dim, self.vdim), self.NORMALISER: (self.n_heads, self.dim),
@@ -97,7 +99,7 @@ class MatrixMemory(_MatrixStateMixer):
 
     def forward(self, x, ctx, cache):
         q, k, v, g = self._split(self.in_proj.forward(x))
-        gates = ops.gemm_f32(x, self.gate_w, self.gate_b)
+        gates = ops.product_f32(x, self.gate_w_stored, self.gate_w, self.gate_b)
         decay, gain, floor = ops.gate_scan(gates, self.gate_cap, cache.state[self.MAXIMUM], ctx, self.n_heads)
         out = ops.linear_recurrence(q, k, v, g, self.norm_w, cache.state[self.STATE], ctx, self.n_heads, self.dim,
                                     self.vdim, self.norm_eps, q_scale=self.q_scale, decay=decay, gain=gain,
