@@ -603,3 +603,29 @@ def test_trace_program_on_a_pusazen_folder(models, tmp_path, dtype):
                 k += 1
             at[e["id"]] = base + len(e["tokens"])
     _assert_logits(got, ref, dtype, f"trace program {dtype}", FRAGILE["B"])
+
+
+def test_command_line_writes_and_runs_a_pusazen_folder(tmp_path):
+    """``random_model`` from a config.json of the design, then ``run_model`` with sampling switched off: the registry,
+    the loader, the engine and the sampler through the command line; the tokens are the plain implementation's."""
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(PUSAZEN["A"][0]))
+    out = tmp_path / "model"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = lambda *a: subprocess.run([sys.executable, "-m", "llm_rs_b200.cli", *a], cwd=root, capture_output=True,
+                                    text=True, timeout=600)
+    assert run("random_model", "--config", str(cfg_path), "--out", str(out), "--seed", "3", "--sigma", "0.15",
+               "--norm-jitter", "0.2").returncode == 0
+    prompt = [5, 17, 3, 9, 200, 41, 7, 7, 150]
+    done = run("run_model", "--model-path", str(out), "--prompt-ids", ",".join(map(str, prompt)), "--dtype", "float32",
+               "--max-new-tokens", "10", "--ignore-eos", "--page-size", "16", "--block-pool-size", "32")
+    assert done.returncode == 0, done.stderr[-2000:]
+    lines = dict(l.split(":", 1) for l in done.stdout.splitlines() if ":" in l)
+    got = [int(t) for t in lines["Generated token ids"].split(",")]
+    cfg, w = P.load_model_dir(str(out))
+    seq = list(prompt)
+    for tok in got:
+        row = P.forward(cfg, w, seq)[-1]
+        assert float(row.max() - row[tok]) <= 1e-4 * float(row.abs().max())
+        seq.append(tok)
+    assert len(got) == 10
