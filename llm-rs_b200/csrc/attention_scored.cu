@@ -15,8 +15,10 @@
 //             angle position * inv_freq[i], made in double), q rewritten in place, k and v written into their pages;
 //   prefill   16 queries of one request per block against the keys they may see, online softmax (any type);
 //             bfloat16 with dk, dv multiples of 16 up to 128: 64 queries per block on the tensor cores (mma.sync);
-//   decode    one query per request: the visible keys are cut into runs that separate blocks take (a warp per key,
-//             lanes over channels), and a second kernel merges the runs and adds the sink.
+//   decode    one query per request: the visible keys are cut into runs that separate blocks take, and a second
+//             kernel merges the runs and adds the sink. Rows that can be read sixteen bytes a load: a block takes up
+//             to four query heads of one key head together, a lane per key for the scores, lanes over channels for
+//             the values. Any other size: a block per query head, a warp per key, lanes over channels.
 // Scores, weights and sums are float32.
 #include "common.cuh"
 #include "mma_util.cuh"
@@ -605,7 +607,21 @@ __host__ __device__ inline size_t sd_part_stride(int dv) { return (size_t)dv + 2
 
 // One block per (decode request, query head, run of keys). Each warp takes four keys of every sixteen of the run: its
 // lanes split the channels, the dot products are summed over the warp, the weights and the sum of values are kept online.
-template <typename T>
+// Four neighbouring channels in one load (8 bytes of bfloat16, 16 of float32).
+__device__ __forceinline__ void load4(const float* p, float* out) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float* out) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
+
+// VEC: head sizes are multiples of four and the rows aligned for it: a lane's register 4 g + e holds channel
+// (lane + 32 g) * 4 + e and a row is read four channels a load. Otherwise register j holds channel lane + 32 j.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(SD_THREADS)
 scored_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ cache,
                      const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
@@ -629,11 +645,22 @@ scored_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __res
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float qr[SD_MAXC], acc[SD_MAXC];
   const T* qp = q + (size_t)q_start[req] * q_stride + (size_t)head * dk;
+  auto channel = [&](int j) { return VEC ? (lane + 32 * (j >> 2)) * 4 + (j & 3) : lane + 32 * j; };
+  auto load_row = [&](const T* row, int width, float* out) {
+    if (VEC) {
 #pragma unroll
-  for (int j = 0; j < SD_MAXC; ++j) {
-    qr[j] = lane + 32 * j < dk ? to_float(qp[lane + 32 * j]) : 0.f;
-    acc[j] = 0.f;
-  }
+      for (int g = 0; g < SD_MAXC / 4; ++g) {
+        if ((lane + 32 * g) * 4 < width) load4(row + (lane + 32 * g) * 4, out + 4 * g);
+        else out[4 * g] = out[4 * g + 1] = out[4 * g + 2] = out[4 * g + 3] = 0.f;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < SD_MAXC; ++j) out[j] = lane + 32 * j < width ? to_float(row[lane + 32 * j]) : 0.f;
+    }
+  };
+  load_row(qp, dk, qr);
+#pragma unroll
+  for (int j = 0; j < SD_MAXC; ++j) acc[j] = 0.f;
   float m = -INFINITY, l = 0.f;
   // Four keys per turn: their rows are all asked for before the first is used, so that a warp has several loads on
   // their way (one key at a time, the kernel waited a memory round trip per key).
@@ -646,11 +673,8 @@ scored_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __res
       const T* kr = cache + page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)(key % page_size) * dk;
       const T* vr = cache + page_head_offset(page, kvh, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk +
                     (size_t)(key % page_size) * dv;
-#pragma unroll
-      for (int j = 0; j < SD_MAXC; ++j) {
-        kf[u][j] = lane + 32 * j < dk ? to_float(kr[lane + 32 * j]) : 0.f;
-        vf[u][j] = lane + 32 * j < dv ? to_float(vr[lane + 32 * j]) : 0.f;
-      }
+      load_row(kr, dk, kf[u]);
+      load_row(vr, dv, vf[u]);
     }
     float sc[SD_UNROLL], m_new = m;
 #pragma unroll
@@ -681,7 +705,7 @@ scored_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __res
   if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
 #pragma unroll
   for (int j = 0; j < SD_MAXC; ++j)
-    if (lane + 32 * j < dv) s_o[warp * dv + lane + 32 * j] = acc[j];
+    if (channel(j) < dv) s_o[warp * dv + channel(j)] = acc[j];
   __syncthreads();
   float mm = -INFINITY;
 #pragma unroll
@@ -696,6 +720,168 @@ scored_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __res
     float ll = 0.f;
 #pragma unroll
     for (int w = 0; w < SD_WARPS; ++w) ll += s_m[w] == -INFINITY ? 0.f : s_l[w] * expf(s_m[w] - mm);
+    pp[0] = mm;
+    pp[1] = ll;
+  }
+}
+
+// Sixteen bytes of a row as floats: eight bfloat16 channels or four float32 ones.
+template <typename T> struct RowChunk;
+template <> struct RowChunk<float> { static constexpr int N = 4; };
+template <> struct RowChunk<bf16> { static constexpr int N = 8; };
+__device__ __forceinline__ void load_chunk(const float* p, float* out) { load4(p, out); }
+__device__ __forceinline__ void load_chunk(const bf16* p, float* out) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 a = __bfloat1622float2(h[i]);
+    out[2 * i] = a.x;
+    out[2 * i + 1] = a.y;
+  }
+}
+
+// The decode kernel for rows that can be read sixteen bytes a load: one block per (decode request, key head, up to GH
+// of the query heads that share it, run of keys), so that a key and a value row are fetched once for all those heads.
+// A warp takes 32 keys a turn. Scores: a LANE per key; it walks its key's row against the queries in shared memory
+// (every lane reads the same query channel: a broadcast), so a score needs no sum over the warp, and the cap and the
+// exponential run once per key and head, not once per lane. Values: the lanes split the channels (VG groups of 4 x 32),
+// a key's weights and the place of its row come from the key's lane by shuffles.
+template <typename T, int GH, int VG>
+__global__ void __launch_bounds__(SD_THREADS)
+scored_decode_grouped_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ cache,
+                             const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
+                             const int* __restrict__ cached_len, const int* __restrict__ block_table,
+                             int table_stride, float* __restrict__ part, int max_splits, int split_keys,
+                             int n_q_heads, int n_kv_heads, int dk, int dv, int page_size, ScoreOpts opt) {
+  constexpr int CW = RowChunk<T>::N;
+  constexpr unsigned FULL = 0xffffffffu;
+  __shared__ float s_m[SD_WARPS][GH], s_l[SD_WARPS][GH];
+  extern __shared__ __align__(16) float sg_smem[];      // queries [GH][dk], then the warps' sums [SD_WARPS][GH][dv]
+  float* q_s = sg_smem;
+  float* s_o = sg_smem + GH * dk;
+  const int G = n_q_heads / n_kv_heads, hgroups = (G + GH - 1) / GH;
+  const int di = blockIdx.x, kvh = blockIdx.y / hgroups, g0 = (blockIdx.y % hgroups) * GH, split = blockIdx.z;
+  const int ng = min(GH, G - g0), head0 = kvh * G + g0;
+  const int req = dec_reqs[di];
+  const int pos = cached_len[req];                  // the new token's key is in the cache already
+  const int lo = first_visible(opt, pos);
+  const int k_begin = lo + split * split_keys, k_end = min(k_begin + split_keys, pos + 1);
+  auto record = [&](int h) { return part + (((size_t)di * n_q_heads + head0 + h) * max_splits + split) * sd_part_stride(dv); };
+  if (k_begin >= k_end) {
+    if (threadIdx.x < ng) {
+      float* pp = record(threadIdx.x);
+      pp[0] = -INFINITY;
+      pp[1] = 0.f;
+    }
+    return;
+  }
+  const int* table = block_table + (size_t)req * table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    const T* qp = q + (size_t)q_start[req] * q_stride + (size_t)head0 * dk;      // heads beyond the group: zeros
+    for (int i = threadIdx.x; i < GH * dk; i += SD_THREADS) q_s[i] = i < ng * dk ? to_float(qp[i]) : 0.f;
+  }
+  __syncthreads();
+  float acc[GH][4 * VG], m[GH], l[GH];
+#pragma unroll
+  for (int h = 0; h < GH; ++h) {
+    m[h] = -INFINITY;
+    l[h] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4 * VG; ++j) acc[h][j] = 0.f;
+  }
+  const size_t head_base = (size_t)kvh * page_size * (dk + dv), page_elems = (size_t)n_kv_heads * page_size * (dk + dv);
+  for (int key0 = k_begin + warp * 32; key0 < k_end; key0 += SD_WARPS * 32) {
+    const bool seen = key0 + lane < k_end;
+    const int key = seen ? key0 + lane : k_end - 1;
+    const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 3, key);
+    const int row = key % page_size;
+    const size_t base = (size_t)page * page_elems + head_base;
+    const T* kr = cache + base + (size_t)row * dk;
+    const size_t v_at = base + (size_t)page_size * dk + (size_t)row * dv;      // this lane's key's value row
+    float dot[GH];
+#pragma unroll
+    for (int h = 0; h < GH; ++h) dot[h] = 0.f;
+#pragma unroll 4
+    for (int c = 0; c < dk; c += CW) {
+      float kf[CW];
+      load_chunk(kr + c, kf);
+#pragma unroll
+      for (int h = 0; h < GH; ++h) {
+#pragma unroll
+        for (int e = 0; e < CW; e += 4) {
+          const float4 qa = *reinterpret_cast<const float4*>(q_s + h * dk + c + e);
+          dot[h] = fmaf(qa.x, kf[e], dot[h]);
+          dot[h] = fmaf(qa.y, kf[e + 1], dot[h]);
+          dot[h] = fmaf(qa.z, kf[e + 2], dot[h]);
+          dot[h] = fmaf(qa.w, kf[e + 3], dot[h]);
+        }
+      }
+    }
+    float p[GH];
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+      const float s = seen ? capped(opt, dot[h]) : -INFINITY;      // lane 0's key always counts
+      const float m_new = fmaxf(m[h], warp_max(s));
+      const float corr = expf(m[h] - m_new);
+      p[h] = seen ? expf(s - m_new) : 0.f;
+      l[h] = l[h] * corr + warp_sum(p[h]);
+      m[h] = m_new;
+#pragma unroll
+      for (int j = 0; j < 4 * VG; ++j) acc[h][j] *= corr;
+    }
+    const unsigned v_lo = (unsigned)v_at, v_hi = (unsigned)(v_at >> 32);
+    const int n_here = min(32, k_end - key0);
+#pragma unroll 4
+    for (int u = 0; u < n_here; ++u) {
+      const size_t at = ((size_t)__shfl_sync(FULL, v_hi, u) << 32) | __shfl_sync(FULL, v_lo, u);
+      const T* vr = cache + at;
+      float vf[4 * VG];
+#pragma unroll
+      for (int g = 0; g < VG; ++g) {
+        if ((lane + 32 * g) * 4 < dv) load4(vr + (lane + 32 * g) * 4, vf + 4 * g);
+        else vf[4 * g] = vf[4 * g + 1] = vf[4 * g + 2] = vf[4 * g + 3] = 0.f;
+      }
+#pragma unroll
+      for (int h = 0; h < GH; ++h) {
+        const float pu = __shfl_sync(FULL, p[h], u);
+#pragma unroll
+        for (int j = 0; j < 4 * VG; ++j) acc[h][j] = fmaf(pu, vf[j], acc[h][j]);
+      }
+    }
+  }
+  // The warps' records of each head become the block's.
+  if (lane == 0) {
+#pragma unroll
+    for (int h = 0; h < GH; ++h) { s_m[warp][h] = m[h]; s_l[warp][h] = l[h]; }
+  }
+#pragma unroll
+  for (int h = 0; h < GH; ++h)
+#pragma unroll
+    for (int j = 0; j < 4 * VG; ++j) {
+      const int c = (lane + 32 * (j >> 2)) * 4 + (j & 3);
+      if (c < dv) s_o[((size_t)warp * GH + h) * dv + c] = acc[h][j];
+    }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ng * dv; i += SD_THREADS) {
+    const int h = i / dv, c = i - h * dv;
+    float mm = -INFINITY, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w) mm = fmaxf(mm, s_m[w][h]);
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w)
+      a += s_m[w][h] == -INFINITY ? 0.f : s_o[((size_t)w * GH + h) * dv + c] * expf(s_m[w][h] - mm);
+    record(h)[2 + c] = a;
+  }
+  if (threadIdx.x < ng) {
+    const int h = threadIdx.x;
+    float mm = -INFINITY, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w) mm = fmaxf(mm, s_m[w][h]);
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w) ll += s_m[w][h] == -INFINITY ? 0.f : s_l[w][h] * expf(s_m[w][h] - mm);
+    float* pp = record(h);
     pp[0] = mm;
     pp[1] = ll;
   }
@@ -726,6 +912,18 @@ __global__ void scored_decode_merge_kernel(const float* __restrict__ part, T* __
   }
 }
 
+// How many query heads of a key head one block of the decode kernel takes (1, 2 or 4), or 0 where rows cannot be read
+// sixteen bytes a load (key rows of a whole number of such loads, value rows of a multiple of four channels) and the
+// kernel of a block per query head runs. Callers size a step's runs of keys by it.
+LLMRS_API int llmrs_scored_decode_group(int n_q_heads, int n_kv_heads, int dk, int dv, int page_size, int dtype) {
+  const int cw = dtype == LLMRS_F32 ? 4 : 8;
+  if (n_kv_heads <= 0 || n_q_heads % n_kv_heads || dk % cw || dv % 4 || dk > 32 * SD_MAXC || dv > 32 * SD_MAXC ||
+      ((long long)page_size * (dk + dv)) % cw)
+    return 0;
+  const int G = n_q_heads / n_kv_heads;
+  return G >= 3 ? 4 : G;
+}
+
 LLMRS_API long long llmrs_scored_decode_scratch_floats(int n_dec, int n_q_heads, int dv, int max_splits) {
   return (long long)n_dec * n_q_heads * max_splits * (long long)sd_part_stride(dv);
 }
@@ -750,18 +948,49 @@ LLMRS_API int llmrs_scored_decode(const void* q, long long q_stride, void* out, 
   ScoreOpts opt{scale, softcap, sink, mask, mask_size};
   dim3 grid(n_dec, n_q_heads, max_splits), mgrid(n_dec, n_q_heads);
   const size_t smem = (size_t)SD_WARPS * dv * sizeof(float);
+  // Rows of a multiple of four channels that start on a load's boundary are read four channels a load.
+  const size_t esz = dtype == LLMRS_F32 ? 4 : 2;
+  const bool vec = dk % 4 == 0 && dv % 4 == 0 && ((uintptr_t)q % (4 * esz)) == 0 && q_stride % 4 == 0 &&
+                   ((uintptr_t)cache % (4 * esz)) == 0;
+  const int gh = llmrs_scored_decode_group(n_q_heads, n_kv_heads, dk, dv, page_size, dtype);
+  const bool grouped = gh > 0 && ((uintptr_t)cache & 15) == 0 && !g_scored_generic_only;
+  const int G = n_q_heads / n_kv_heads;
+  dim3 ggrid(n_dec, grouped ? n_kv_heads * ((G + gh - 1) / gh) : 1, max_splits);
+  const size_t gsmem = grouped ? ((size_t)gh * dk + (size_t)SD_WARPS * gh * dv) * sizeof(float) : 0;
+  LLMRS_REQUIRE(ggrid.y <= 65535, "scored_decode: too many head groups");
+#define LLMRS_SG_LAUNCH(T, GH, VG)                                                                                    \
+  scored_decode_grouped_kernel<T, GH, VG><<<ggrid, SD_THREADS, gsmem, stream>>>(                                      \
+      (const T*)q, q_stride, (const T*)cache, dec_reqs, q_start, cached_len, block_table, table_stride, scratch,      \
+      max_splits, split_keys, n_q_heads, n_kv_heads, dk, dv, page_size, opt)
+#define LLMRS_SD_LAUNCH(T)                                                                                            \
+  do {                                                                                                                \
+    if (grouped) {                                                                                                    \
+      if (dv <= 128) {                                                                                                \
+        if (gh == 1) LLMRS_SG_LAUNCH(T, 1, 1);                                                                        \
+        else if (gh == 2) LLMRS_SG_LAUNCH(T, 2, 1);                                                                   \
+        else LLMRS_SG_LAUNCH(T, 4, 1);                                                                                \
+      } else {                                                                                                        \
+        if (gh == 1) LLMRS_SG_LAUNCH(T, 1, 2);                                                                        \
+        else if (gh == 2) LLMRS_SG_LAUNCH(T, 2, 2);                                                                   \
+        else LLMRS_SG_LAUNCH(T, 4, 2);                                                                                \
+      }                                                                                                               \
+    } else if (vec)                                                                                                   \
+      scored_decode_kernel<T, true><<<grid, SD_THREADS, smem, stream>>>(                                              \
+          (const T*)q, q_stride, (const T*)cache, dec_reqs, q_start, cached_len, block_table, table_stride, scratch,  \
+          max_splits, split_keys, n_q_heads, n_kv_heads, dk, dv, page_size, opt);                                     \
+    else                                                                                                              \
+      scored_decode_kernel<T, false><<<grid, SD_THREADS, smem, stream>>>(                                             \
+          (const T*)q, q_stride, (const T*)cache, dec_reqs, q_start, cached_len, block_table, table_stride, scratch,  \
+          max_splits, split_keys, n_q_heads, n_kv_heads, dk, dv, page_size, opt);                                     \
+  } while (0)
   if (dtype == LLMRS_F32) {
-    scored_decode_kernel<float><<<grid, SD_THREADS, smem, stream>>>(
-        (const float*)q, q_stride, (const float*)cache, dec_reqs, q_start, cached_len, block_table, table_stride,
-        scratch, max_splits, split_keys, n_q_heads, n_kv_heads, dk, dv, page_size, opt);
+    LLMRS_SD_LAUNCH(float);
     int rc = llmrs_launch_status("scored_decode");
     if (rc) return rc;
     scored_decode_merge_kernel<float><<<mgrid, 64, 0, stream>>>(scratch, (float*)out, out_stride, dec_reqs, q_start,
                                                                 max_splits, n_q_heads, dv, sink);
   } else if (dtype == LLMRS_BF16) {
-    scored_decode_kernel<bf16><<<grid, SD_THREADS, smem, stream>>>(
-        (const bf16*)q, q_stride, (const bf16*)cache, dec_reqs, q_start, cached_len, block_table, table_stride,
-        scratch, max_splits, split_keys, n_q_heads, n_kv_heads, dk, dv, page_size, opt);
+    LLMRS_SD_LAUNCH(bf16);
     int rc = llmrs_launch_status("scored_decode");
     if (rc) return rc;
     scored_decode_merge_kernel<bf16><<<mgrid, 64, 0, stream>>>(scratch, (bf16*)out, out_stride, dec_reqs, q_start,
@@ -769,5 +998,7 @@ LLMRS_API int llmrs_scored_decode(const void* q, long long q_stride, void* out, 
   } else {
     return llmrs_fail("scored_decode: unknown dtype %d", dtype);
   }
+#undef LLMRS_SD_LAUNCH
+#undef LLMRS_SG_LAUNCH
   return llmrs_launch_status("scored_decode (merge)");
 }

@@ -1113,6 +1113,12 @@ def scored_prefill(q, out, cache, tiles, n_tiles: int, ctx, table, n_q_heads: in
         dtype_code(q.dtype), q.size(0), cache.size(0), int(prefer_tc), _stream()), "scored_prefill")
 
 
+def scored_decode_group(n_q_heads: int, n_kv_heads: int, dk: int, dv: int, page_size: int, dtype: torch.dtype) -> int:
+    """Query heads of one key head that a block of the decode kernel takes together (1, 2 or 4), or 0 where the rows
+    cannot be read sixteen bytes a load and a block takes one query head with a warp per key."""
+    return int(_lib().llmrs_scored_decode_group(n_q_heads, n_kv_heads, dk, dv, page_size, dtype_code(dtype)))
+
+
 def scored_decode(q, out, cache, dec_reqs, n_dec: int, ctx, table, max_splits: int, split_keys: int, n_q_heads: int,
                   n_kv_heads: int, dk: int, dv: int, page_size: int, scale: float, softcap: float, sink, mask: int,
                   mask_size: int) -> None:

@@ -13,7 +13,9 @@ from .registry import register
 from .spec import CacheNeed, WeightSpec
 
 MASKS = {"causal": ops.MASK_CAUSAL, "window": ops.MASK_WINDOW, "chunk": ops.MASK_CHUNK}
-DECODE_SPLIT_KEYS = 64      # keys per block of the decode kernel at least; doubled while a step has too many blocks
+# Keys per block of the decode kernel at least, doubled while a step has too many blocks: a block of the kernel that
+# takes a key head's query heads together walks 128 keys a turn (a lane per key), the kernel of a warp per key 16.
+DECODE_SPLIT_KEYS = {True: 128, False: 64}
 DECODE_MAX_BLOCKS = 8192
 
 
@@ -137,8 +139,11 @@ class ScoredAttention(Mixer):
                                prefer_tc=bool(plan.values["long_portions"]) and _ATTN_TC)
         if n_decode:
             span = max(1, min(max_kv, self.mask_size) if self.mask_size else max_kv)   # keys a query can see at most
-            split_keys = DECODE_SPLIT_KEYS
-            while n_decode * self.n_heads * -(-span // split_keys) > DECODE_MAX_BLOCKS and split_keys < 4096:
+            group = ops.scored_decode_group(self.n_heads, self.n_kv_heads, self.dim, self.vdim, cache.page_size, q.dtype)
+            split_keys = DECODE_SPLIT_KEYS[group > 0]
+            blocks = n_decode * self.n_kv_heads * -(-(self.n_heads // self.n_kv_heads) // group) if group else \
+                n_decode * self.n_heads
+            while blocks * -(-span // split_keys) > DECODE_MAX_BLOCKS and split_keys < 4096:
                 split_keys *= 2
             ops.scored_decode(q, out, pages, plan.arrays["decode_reqs"], n_decode, ctx, table, -(-span // split_keys),
                               split_keys, *args)

@@ -441,6 +441,71 @@ def test_a_far_key_among_hundreds_and_the_sink(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv,dk,dv,page,group", [(3, 1, 64, 256, 16, (4, 4)), (6, 2, 128, 128, 32, (4, 4)),
+                                                        (8, 1, 16, 8, 8, (4, 4)), (4, 4, 200, 36, 16, (1, 1)),
+                                                        (4, 2, 24, 12, 4, (2, 2)), (5, 5, 20, 12, 16, (1, 0))])
+def test_decode_kernels_alone(dtype, heads, kv, dk, dv, page, group):
+    """Single queries against cached rows over scattered pages, by the kernel that takes a key head's query heads
+    together with a lane per key, and by the kernel of a block per query head with a warp per key. The newest
+    positions sit at 0, just below, on and just above the 32 keys of a warp's turn, the 128 of a block's turn and a
+    run's end, and hundreds further; runs of 128 and 256 keys; no mask, chunks and a window, with a cap and a sink.
+    Against a softmax written out in float64."""
+    from llm_rs_b200 import ops
+    assert ops.scored_decode_group(heads, kv, dk, dv, page, dtype) == group[dtype == torch.bfloat16]
+    g = torch.Generator().manual_seed(heads * 31 + dk)
+    positions = [0, 1, 30, 31, 32, 33, 127, 128, 129, 255, 256, 257, 700]
+    R, width = len(positions), -(-701 // page)
+    n_pages = sum(-(-(p + 1) // page) for p in positions) + 3
+    pages = torch.randn(n_pages, kv, page * (dk + dv), generator=g).to(dtype)
+    q = (1.5 * torch.randn(R, heads * dk, generator=g)).to(dtype)
+    sink = torch.randn(heads, generator=g)
+    perm, table, at = torch.randperm(n_pages, generator=g).tolist(), torch.zeros(R, width, dtype=torch.int32), 0
+    for r, p in enumerate(positions):
+        n = -(-(p + 1) // page)
+        table[r, :n] = torch.tensor(perm[at:at + n], dtype=torch.int32)
+        at += n
+    scale, cap, G = 0.8 / math.sqrt(dk), 5.0, heads // kv
+
+    def expected(mask, size):
+        out = torch.zeros(R, heads * dv, dtype=torch.float64)
+        for r, p in enumerate(positions):
+            lo = 0 if mask == ops.MASK_CAUSAL else (p // size) * size if mask == ops.MASK_CHUNK else max(0, p - size + 1)
+            rows = pages[table[r, : p // page + 1].long()].double()                      # [pages, kv, page * (dk + dv)]
+            keys = rows[:, :, : page * dk].reshape(-1, kv, page, dk).transpose(1, 2).reshape(-1, kv, dk)[lo: p + 1]
+            vals = rows[:, :, page * dk:].reshape(-1, kv, page, dv).transpose(1, 2).reshape(-1, kv, dv)[lo: p + 1]
+            for h in range(heads):
+                sc = keys[:, h // G] @ q[r, h * dk:(h + 1) * dk].double() * scale
+                sc = cap * torch.tanh(sc / cap)
+                top = max(sc.max().item(), sink[h].item())
+                e = torch.exp(sc - top)
+                out[r, h * dv:(h + 1) * dv] = (e[:, None] * vals[:, h // G]).sum(0) / (e.sum() + math.exp(sink[h].item() - top))
+        return out
+
+    class Ctx(SimpleNamespace):
+        def scratch(self, name, n):
+            return torch.full((max(n, 1),), float("nan"), device=DEV)
+    ctx = Ctx(q_start=torch.arange(R, dtype=torch.int32, device=DEV),
+              cached_len=torch.tensor(positions, dtype=torch.int32, device=DEV))
+    reqs = torch.arange(R, dtype=torch.int32, device=DEV)
+    qd, pd, td, sd = q.to(DEV), pages.to(DEV), table.to(DEV), sink.to(DEV)
+    try:
+        for mask, size in ((ops.MASK_CAUSAL, 0), (ops.MASK_CHUNK, 96), (ops.MASK_CHUNK, 300), (ops.MASK_WINDOW, 130)):
+            want = expected(mask, size)
+            span = min(701, size) if size else 701
+            for per_head in (False, True):
+                ops.scored_generic_only(per_head)
+                for split in (128, 256):
+                    out = torch.full((R, heads * dv), float("nan"), dtype=dtype, device=DEV)
+                    ops.scored_decode(qd, out, pd, reqs, R, ctx, td, -(-span // split), split, heads, kv, dk, dv, page,
+                                      scale, cap, sd, mask, size)
+                    d = (out.double().cpu() - want).abs().max().item()
+                    assert d <= (2e-5 if dtype == torch.float32 else 1e-2) * want.abs().max().item(), \
+                        (mask, size, per_head, split, d)
+    finally:
+        ops.scored_generic_only(False)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,shared,n_tokens", [(4, 2, 24, 50), (3, 3, 0, 7), (1, 1, 8, 5), (37, 4, 16, 300),
                                                          (8, 1, 0, 1), (12, 3, 128, 260), (200, 6, 0, 40)])
 def test_routed_experts_against_plain(dtype, experts, top, shared, n_tokens):
