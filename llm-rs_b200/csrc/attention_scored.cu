@@ -741,6 +741,15 @@ __device__ __forceinline__ void load_chunk(const bf16* p, float* out) {
   }
 }
 
+// Asks for a row's 128-byte lines to be brought into the L2 (no register, no wait).
+template <typename T>
+__device__ __forceinline__ void prefetch_row_l2(const T* row, int width) {
+  const char* p = reinterpret_cast<const char*>(row);
+  const char* end = p + (size_t)width * sizeof(T);
+  for (const char* line = p - ((uintptr_t)p & 127); line < end; line += 128)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+}
+
 // The decode kernel for rows that can be read sixteen bytes a load: one block per (decode request, key head, up to GH
 // of the query heads that share it, run of keys), so that a key and a value row are fetched once for all those heads.
 // A warp takes 32 keys a turn. Scores: a LANE per key; it walks its key's row against the queries in shared memory
@@ -755,8 +764,9 @@ scored_decode_grouped_kernel(const T* __restrict__ q, long long q_stride, const 
                              int table_stride, float* __restrict__ part, int max_splits, int split_keys,
                              int n_q_heads, int n_kv_heads, int dk, int dv, int page_size, ScoreOpts opt) {
   constexpr int CW = RowChunk<T>::N;
-  constexpr unsigned FULL = 0xffffffffu;
   __shared__ float s_m[SD_WARPS][GH], s_l[SD_WARPS][GH];
+  __shared__ __align__(16) float s_p[SD_WARPS][32][GH];      // a turn's weights, [key][head]
+  __shared__ unsigned long long s_at[SD_WARPS][32];          // where each key's value row starts
   extern __shared__ __align__(16) float sg_smem[];      // queries [GH][dk], then the warps' sums [SD_WARPS][GH][dv]
   float* q_s = sg_smem;
   float* s_o = sg_smem + GH * dk;
@@ -800,6 +810,13 @@ scored_decode_grouped_kernel(const T* __restrict__ q, long long q_stride, const 
     const size_t base = (size_t)page * page_elems + head_base;
     const T* kr = cache + base + (size_t)row * dk;
     const size_t v_at = base + (size_t)page_size * dk + (size_t)row * dv;      // this lane's key's value row
+    // Asked for now, the value rows of this turn and the key row of the warp's next turn are in the L2 when wanted.
+    if (seen) prefetch_row_l2(cache + v_at, dv);
+    if (key0 + lane + SD_WARPS * 32 < k_end) {
+      const int nk = key0 + lane + SD_WARPS * 32;
+      const int np = LLMRS_CHECKED_PAGE(table[nk / page_size], 3, nk);
+      prefetch_row_l2(cache + (size_t)np * page_elems + head_base + (size_t)(nk % page_size) * dk, dk);
+    }
     float dot[GH];
 #pragma unroll
     for (int h = 0; h < GH; ++h) dot[h] = 0.f;
@@ -831,12 +848,17 @@ scored_decode_grouped_kernel(const T* __restrict__ q, long long q_stride, const 
 #pragma unroll
       for (int j = 0; j < 4 * VG; ++j) acc[h][j] *= corr;
     }
-    const unsigned v_lo = (unsigned)v_at, v_hi = (unsigned)(v_at >> 32);
+    // The weights and the rows' places go through shared memory: two broadcast reads a key, where shuffles would be
+    // two for the place and one per head.
+    __syncwarp();
+#pragma unroll
+    for (int h = 0; h < GH; ++h) s_p[warp][lane][h] = p[h];
+    s_at[warp][lane] = v_at;
+    __syncwarp();
     const int n_here = min(32, k_end - key0);
-#pragma unroll 4
+#pragma unroll 8
     for (int u = 0; u < n_here; ++u) {
-      const size_t at = ((size_t)__shfl_sync(FULL, v_hi, u) << 32) | __shfl_sync(FULL, v_lo, u);
-      const T* vr = cache + at;
+      const T* vr = cache + s_at[warp][u];
       float vf[4 * VG];
 #pragma unroll
       for (int g = 0; g < VG; ++g) {
@@ -845,7 +867,7 @@ scored_decode_grouped_kernel(const T* __restrict__ q, long long q_stride, const 
       }
 #pragma unroll
       for (int h = 0; h < GH; ++h) {
-        const float pu = __shfl_sync(FULL, p[h], u);
+        const float pu = s_p[warp][u][h];
 #pragma unroll
         for (int j = 0; j < 4 * VG; ++j) acc[h][j] = fmaf(pu, vf[j], acc[h][j]);
       }
